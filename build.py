@@ -1,11 +1,13 @@
 #!/usr/bin/env python3
 """Build the native libraries in-tree (no pip, no JIT cache):
 
-  distributed-llama-multiusers_b200/lib/libdllama_b200_cuda.so   nvcc, sm_100a only
+  distributed-llama-multiusers_b200/lib/libdllama_b200_cuda.so   nvcc, sm_100a only: the Q40 / f32 Llama kernels
+  distributed-llama-multiusers_b200/lib/libdllama_b200_layers.so nvcc, sm_100a only: the kernels of layer-list models
+                                                                 (dense bf16 / f32 weights, latent attention, Mamba-2)
   distributed-llama-multiusers_b200/lib/libdllama_b200_host.so   g++, CPU runtime (tokenizer,
                                                                  sampler, codecs, scheduler ...)
 
-Usage: python build.py [--force] [--verbose]
+Usage: python build.py [--force] [--verbose] [cuda|layers|host ...]   (no target: all three)
 Objects are rebuilt only when a source or header is newer (so repeated calls are cheap).
 """
 from __future__ import annotations
@@ -59,13 +61,28 @@ def _run(cmd, verbose, log_path=None):
         sys.stdout.write(p.stdout)
 
 
+# sources of the layer-list model library; prep.cu (error plumbing, argmax) and sampler.cu are shared with the other
+# one (their objects are compiled once), the rest belongs to this library alone
+LAYERS_OWN = ["dense.cu", "latent_attention.cu", "mamba2.cu", "norms.cu"]
+LAYERS_SHARED = ["prep.cu", "sampler.cu"]
+
+
 def build_cuda(force=False, verbose=False) -> str:
+    srcs = sorted(f for f in os.listdir(CUDA_SRC) if f.endswith(".cu") and f not in LAYERS_OWN)
+    return _build_cuda_lib("libdllama_b200_cuda.so", srcs, force, verbose)
+
+
+def build_layers(force=False, verbose=False) -> str:
+    """Only what a layer-list model needs: a fresh checkout serves one without compiling the Q40 kernels."""
+    return _build_cuda_lib("libdllama_b200_layers.so", sorted(LAYERS_OWN + LAYERS_SHARED), force, verbose)
+
+
+def _build_cuda_lib(name, srcs, force, verbose) -> str:
     nvcc = _find_nvcc()
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB, exist_ok=True)
     headers = [os.path.join(CUDA_SRC, f) for f in os.listdir(CUDA_SRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(ROOT, "include", "dllama_b200.h"))
-    srcs = sorted(f for f in os.listdir(CUDA_SRC) if f.endswith(".cu"))
     objs, jobs = [], []
     for s in srcs:
         src = os.path.join(CUDA_SRC, s)
@@ -75,7 +92,7 @@ def build_cuda(force=False, verbose=False) -> str:
             jobs.append(([nvcc] + NVCC_FLAGS + ["-c", src, "-o", obj], obj[:-2] + ".ptxas.log"))
     with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         list(ex.map(lambda j: _run(j[0], verbose, j[1]), jobs))
-    out = os.path.join(LIB, "libdllama_b200_cuda.so")
+    out = os.path.join(LIB, name)
     if force or jobs or _newer(out, objs):
         _run([nvcc, "-shared", "-o", out] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"], verbose)
     return out
@@ -106,9 +123,18 @@ def build_host(force=False, verbose=False) -> str:
 
 
 def build_all(force=False, verbose=False):
-    return build_cuda(force, verbose), build_host(force, verbose)
+    cuda = build_cuda(force, verbose)
+    build_layers(False, verbose)          # after the first library: the shared objects are fresh by now
+    return cuda, build_host(force, verbose)
 
 
 if __name__ == "__main__":
-    a, b = build_all("--force" in sys.argv, "--verbose" in sys.argv)
-    print("built:", a, b)
+    force, verbose = "--force" in sys.argv, "--verbose" in sys.argv
+    targets = [a for a in sys.argv[1:] if not a.startswith("-")]
+    if not targets:
+        a, b = build_all(force, verbose)
+        print("built:", a, b, os.path.join(LIB, "libdllama_b200_layers.so"))
+    else:
+        fns = {"cuda": build_cuda, "layers": build_layers, "host": build_host}
+        for t in targets:
+            print("built:", fns[t](force, verbose))

@@ -12,7 +12,8 @@ Options: --buffer-float-type {f32,f16,q40,q80}, --workers host:port ..., --port,
 --steps, --temperature, --topp, --seed, --chat-template {llama2,llama3,deepSeek3}, --max-seq-len,
 --gpu-index, --gpu-segments a:b, --net-turbo {0,1}; unknown options raise (src/app.cpp:131-133).
 New here: --max-batch (rows per forward / concurrent users), --n-slots, --device {auto,cuda,cpu},
---api-backend {native,python} (dllama-api front end: the C++ epoll server or the Python one).
+--api-backend {native,python} (dllama-api front end: the C++ epoll server or the Python one),
+--dtype {bfloat16,float32} (model directories, i.e. config.json + model.safetensors, chosen by models/registry.py).
 
 Multi-GPU: every node is one process on one GPU of the same NVSwitch box.  Two equivalent ways to
 start them: (a) the reference's way -- ``dllama worker --port P`` per extra GPU, then the root with
@@ -62,6 +63,7 @@ class AppArgs:
     n_slots: int = 0
     device: str = "auto"
     api_backend: str = "native"
+    dtype: str = "bfloat16"     # model directories: bfloat16 (weights, caches, matmul operands) or float32
     benchmark: bool = False
 
     @staticmethod
@@ -114,6 +116,10 @@ class AppArgs:
             elif name == "--max-batch": a.max_batch = int(value)
             elif name == "--n-slots": a.n_slots = int(value)
             elif name == "--device": a.device = value
+            elif name == "--dtype":
+                if value not in ("bfloat16", "float32"):
+                    raise ValueError(f"Invalid dtype: {value}")
+                a.dtype = value
             elif name == "--api-backend":
                 if value not in ("native", "python"):
                     raise ValueError(f"Invalid API backend: {value}")
@@ -132,7 +138,8 @@ class AppArgs:
 USAGE = """Usage:
   dllama {inference|chat|worker} [options]       dllama-api [options]
 Options:
-  --model <path.m> --tokenizer <path.t> --prompt <text> --steps <n>
+  --model <path.m | model directory> --tokenizer <path.t> --prompt <text> --steps <n>
+  --dtype {bfloat16,float32}   (model directories: config.json + model.safetensors)
   --buffer-float-type {f32,f16,q40,q80}   --max-seq-len <n>   --temperature <f> --topp <f> --seed <n>
   --workers <host:port> ...   --port <n>   --chat-template {llama2,llama3,deepSeek3}
   --max-batch <rows>  --n-slots <sequences>  --gpu-index <i>  --device {auto,cuda,cpu,cpu-oracle}
@@ -211,8 +218,19 @@ def use_cuda_device(device: str) -> bool:
 
 
 def build_engine(model_path: str, rank: int, world: int, max_batch: int, n_slots: int, max_seq_len: int,
-                 sync_type: int, device: str = "auto", gpu_index: int = -1, workers=(), n_threads: int = 0):
+                 sync_type: int, device: str = "auto", gpu_index: int = -1, workers=(), n_threads: int = 0,
+                 dtype: str = "bfloat16"):
     import torch
+    from ..models import registry
+    if registry.is_model_dir(model_path):
+        # a model directory (config.json + model.safetensors): the engine its architecture names, in --dtype
+        if not use_cuda_device(device):
+            raise ValueError("model directories run on a GPU (no host backend for their layers)")
+        if gpu_index >= 0:
+            torch.cuda.set_device(gpu_index)
+        return registry.engine_for_dir(model_path, rank=rank, world=world, max_rows=max_batch,
+                                       n_slots=n_slots or max(2, min(max_batch, 64)), max_seq_len=max_seq_len or 4096,
+                                       dtype=dtype)
     from ..formats.mfile import read_header
     h = read_header(model_path, max_seq_len)
     if world > h.n_kv_heads:
@@ -324,7 +342,7 @@ class InferenceContext:
         print(f"📄 SpecialVocabSize: {self.tokenizer.special_vocab_size}")
         self.engine = build_engine(args.model_path, self.rank, self.world, args.max_batch, args.n_slots,
                                    args.max_seq_len, args.sync_type, args.device, args.gpu_index, args.workers,
-                                   args.n_threads)
+                                   args.n_threads, args.dtype)
         self.header = self.engine.h
         print(self.header.describe(), flush=True)
         try:

@@ -1,0 +1,235 @@
+// Dense (unquantised) weights: embedding gather and  Y[M][N] = epi(X[M][K] . W[N][K]^T)  for bf16 or f32 weights,
+// f32 activations, f32 accumulation.  Two kernels: a weight-streaming one for up to 8 rows (decode: every weight
+// byte is read once, lanes stride K) and a shared-memory tiled one for more rows.  Both take a batch dimension
+// (grid.z) with element strides, which is how per-head products (a head's slice of a weight against a head's slice
+// of the activations) run as one launch.  In bf16 mode (`round_x`) the activation operand is rounded to bf16 on
+// load, so products are exact in f32 and only the accumulation order differs from a tensor-core product.
+//
+// Epilogues (what other models of this library fuse into their matmul kernels too): plain store, relu(.)^2,
+// aux * sigmoid(.) (an output gate), cap * tanh(. / cap) (logit soft-capping).
+#include "layer_common.cuh"
+#include "../../../include/dllama_b200.h"
+
+__device__ __forceinline__ float dense_epi(float acc, int epi, float aux, float param) {
+    switch (epi) {
+        case DL_DENSE_RELU2: { const float r = fmaxf(acc, 0.f); return r * r; }
+        case DL_DENSE_SIGMOID_MUL: return aux * sigmoid_f(acc);
+        case DL_DENSE_SOFTCAP: return param * tanhf(acc / param);
+        default: return acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// embedding gather: x[m] = table[tokens[m]]
+// ------------------------------------------------------------------------------------------------
+template <typename WT>
+__global__ void embed_rows_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int dim) {
+    const int m = blockIdx.x;
+    const WT* src = table + (size_t)tokens[m] * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) x[(size_t)m * dim + i] = ld_f(src + i);
+}
+
+extern "C" int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (wtype == DL_T_BF16) embed_rows_kernel<<<M, 128, 0, st>>>((const __nv_bfloat16*)table, tokens, x, dim);
+    else embed_rows_kernel<<<M, 128, 0, st>>>((const float*)table, tokens, x, dim);
+    LAYER_CHECK_LAUNCH("dl_embed_rows");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// rows <= 8: one warp per output column, lanes stride K, MT accumulators per lane
+// ------------------------------------------------------------------------------------------------
+#define GV_WARPS 8
+
+template <typename WT, int MT, bool RX>
+__global__ void __launch_bounds__(GV_WARPS * 32) dense_gemv_kernel(DlDenseArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GV_WARPS + warp;
+    const int b = blockIdx.z;
+    if (n >= a.N) return;
+    const WT* w = (const WT*)a.W + (size_t)b * a.w_bs + (size_t)n * a.ldw;
+    const float* x = a.X + (size_t)b * a.x_bs;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+    for (int k = lane; k < a.K; k += 32) {
+        const float wv = ld_f(w + k);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < a.M) {
+                float xv = x[(size_t)m * a.ldx + k];
+                if (RX) xv = round_bf16(xv);
+                acc[m] = fmaf(xv, wv, acc[m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < a.M) {
+                const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
+                a.Y[(size_t)b * a.y_bs + (size_t)m * a.ldy + n] = dense_epi(acc[m], a.epi, aux, a.param);
+            }
+        }
+    }
+}
+
+// vectorised variant: K % 8 == 0, rows 16-byte aligned (checked on the host)
+template <typename WT> struct WVec;
+template <> struct WVec<float> {
+    static __device__ __forceinline__ void load8(const float* p, float* o) {
+        const float4 u = *reinterpret_cast<const float4*>(p), v = *reinterpret_cast<const float4*>(p + 4);
+        o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w; o[4] = v.x; o[5] = v.y; o[6] = v.z; o[7] = v.w;
+    }
+};
+template <> struct WVec<__nv_bfloat16> {
+    static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* o) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const uint32_t r[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(r[i] << 16);
+            o[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+        }
+    }
+};
+
+template <typename WT, int MT, bool RX>
+__global__ void __launch_bounds__(GV_WARPS * 32) dense_gemv_vec_kernel(DlDenseArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * GV_WARPS + warp;
+    const int b = blockIdx.z;
+    if (n >= a.N) return;
+    const WT* w = (const WT*)a.W + (size_t)b * a.w_bs + (size_t)n * a.ldw;
+    const float* x = a.X + (size_t)b * a.x_bs;
+    float acc[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+    for (int k = lane * 8; k < a.K; k += 256) {
+        float wv[8];
+        WVec<WT>::load8(w + k, wv);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < a.M) {
+                float xv[8];
+                WVec<float>::load8(x + (size_t)m * a.ldx + k, xv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[m] = fmaf(RX ? round_bf16(xv[i]) : xv[i], wv[i], acc[m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < a.M) {
+                const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
+                a.Y[(size_t)b * a.y_bs + (size_t)m * a.ldy + n] = dense_epi(acc[m], a.epi, aux, a.param);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// more rows: 64 x 64 output tile per CTA, 16-wide K steps through shared memory, 4 x 4 outputs per thread
+// ------------------------------------------------------------------------------------------------
+#define GT_BM 64
+#define GT_BN 64
+#define GT_BK 16
+
+template <typename WT, bool RX>
+__global__ void __launch_bounds__(256) dense_tile_kernel(DlDenseArgs a) {
+    __shared__ float Xs[GT_BK][GT_BM + 1];
+    __shared__ float Ws[GT_BK][GT_BN + 1];
+    const int b = blockIdx.z;
+    const WT* W = (const WT*)a.W + (size_t)b * a.w_bs;
+    const float* X = a.X + (size_t)b * a.x_bs;
+    const int m0 = blockIdx.y * GT_BM, n0 = blockIdx.x * GT_BN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < a.K; k0 += GT_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 4, k = idx & 15;
+            float xv = 0.f, wv = 0.f;
+            if (k0 + k < a.K) {
+                if (m0 + r < a.M) xv = X[(size_t)(m0 + r) * a.ldx + k0 + k];
+                if (n0 + r < a.N) wv = ld_f(W + (size_t)(n0 + r) * a.ldw + k0 + k);
+            }
+            Xs[k][r] = RX ? round_bf16(xv) : xv;
+            Ws[k][r] = wv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GT_BK; ++k) {
+            float xr[4], wr[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { xr[i] = Xs[k][ty * 4 + i]; wr[i] = Ws[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xr[i], wr[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= a.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= a.N) continue;
+            const float aux = a.aux ? a.aux[(size_t)b * a.aux_bs + (size_t)m * a.ld_aux + n] : 0.f;
+            a.Y[(size_t)b * a.y_bs + (size_t)m * a.ldy + n] = dense_epi(acc[i][j], a.epi, aux, a.param);
+        }
+    }
+}
+
+template <typename WT, bool RX>
+static void launch_dense(const DlDenseArgs& a, cudaStream_t st) {
+    if (a.M <= 8) {
+        const bool vec = a.K % 8 == 0 && a.ldw % 8 == 0 && a.w_bs % 8 == 0 && a.ldx % 4 == 0 && a.x_bs % 4 == 0 &&
+                         ((uintptr_t)a.W & 15) == 0 && ((uintptr_t)a.X & 15) == 0;
+        dim3 grid((a.N + GV_WARPS - 1) / GV_WARPS, 1, a.batch);
+        const int mt = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
+#define GV_CASE(MT_)                                                                                   \
+    case MT_:                                                                                          \
+        if (vec) dense_gemv_vec_kernel<WT, MT_, RX><<<grid, GV_WARPS * 32, 0, st>>>(a);                \
+        else dense_gemv_kernel<WT, MT_, RX><<<grid, GV_WARPS * 32, 0, st>>>(a);                        \
+        break;
+        switch (mt) { GV_CASE(1) GV_CASE(2) GV_CASE(4) GV_CASE(8) }
+#undef GV_CASE
+    } else {
+        dim3 grid((a.N + GT_BN - 1) / GT_BN, (a.M + GT_BM - 1) / GT_BM, a.batch);
+        dense_tile_kernel<WT, RX><<<grid, 256, 0, st>>>(a);
+    }
+}
+
+extern "C" int dl_dense(const DlDenseArgs* args, void* stream) {
+    const DlDenseArgs& a = *args;
+    if (a.M < 1 || a.N < 1 || a.K < 1 || a.batch < 1) { dl_set_error("dl_dense: empty problem"); return -1; }
+    if (a.epi == DL_DENSE_SIGMOID_MUL && a.aux == nullptr) { dl_set_error("dl_dense: the gate epilogue needs aux"); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a.wtype == DL_T_BF16) {
+        if (a.round_x) launch_dense<__nv_bfloat16, true>(a, st);
+        else launch_dense<__nv_bfloat16, false>(a, st);
+    } else if (a.wtype == DL_T_F32) {
+        if (a.round_x) launch_dense<float, true>(a, st);
+        else launch_dense<float, false>(a, st);
+    } else {
+        dl_set_error("dl_dense: unknown weight type %d", a.wtype);
+        return -1;
+    }
+    LAYER_CHECK_LAUNCH("dl_dense");
+    return 0;
+}

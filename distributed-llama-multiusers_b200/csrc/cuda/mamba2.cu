@@ -1,0 +1,141 @@
+// Mamba-2 mixer (a selective state-space recurrence with a scalar decay per head):
+//     xBC_t  = silu(conv_taps(xBC)_t + bias)                 short causal convolution per channel
+//     dt_t   = softplus(dt_t + dt_bias_h)
+//     S_t    = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t B_t x_t^T          S: [state][vdim] per head, f32
+//     y_t    = S_t^T C_t + D_h x_t
+// Per sequence slot the recurrent state S and the last taps-1 convolution inputs live in f32 device pools; a batch
+// is any mix of sequences, each with one or more consecutive rows (a prompt portion, or one decoded token), described
+// by a row list per sequence.  A sequence whose first row of the batch is position 0 starts from zeros, whatever its
+// slot held before.
+//
+// Kernels: the convolution over batch rows + carried inputs, the update of the carried inputs, and the scan
+// (one CTA per sequence and head, the state in shared memory, tokens in order).
+#include "layer_common.cuh"
+#include "../../../include/dllama_b200.h"
+
+#define MB_MAX_TAPS 8
+
+// input of channel ch at position q of sequence n, where the batch holds positions p0 .. p0+len-1 of the sequence
+__device__ __forceinline__ float conv_input(const DlMambaBatch& b, const float* __restrict__ in, long long ld, int in_off,
+                                            const float* __restrict__ conv_state, int channels, int taps,
+                                            int n, int q, int ch) {
+    if (q < 0) return 0.f;
+    const int p0 = b.seq_pos0[n];
+    if (q >= p0) {
+        const int row = b.seq_rows[b.seq_start[n] + (q - p0)];
+        return in[(size_t)row * ld + in_off + ch];
+    }
+    const int k = q - p0 + (taps - 1);                // carried inputs hold positions p0-(taps-1) .. p0-1
+    return conv_state[((size_t)b.seq_slot[n] * (taps - 1) + k) * channels + ch];
+}
+
+// out[row][ch] = silu(bias[ch] + sum_k w[ch][k] * input(pos - (taps-1) + k))
+template <typename WT>
+__global__ void __launch_bounds__(256) mamba_conv_kernel(DlMambaBatch b, const float* __restrict__ in, long long ld, int in_off,
+                                                         const WT* __restrict__ w, const WT* __restrict__ bias,
+                                                         const float* __restrict__ conv_state, float* __restrict__ out,
+                                                         int channels, int taps) {
+    const int m = blockIdx.x;
+    const int n = b.row_seq[m], pos = b.pos[m];
+    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
+        float acc = ld_f(bias + ch);
+        for (int k = 0; k < taps; ++k)
+            acc = fmaf(ld_f(w + (size_t)ch * taps + k), conv_input(b, in, ld, in_off, conv_state, channels, taps, n, pos - (taps - 1) + k, ch), acc);
+        out[(size_t)m * channels + ch] = silu_f(acc);
+    }
+}
+
+// carried inputs after the batch: positions last-(taps-2) .. last of each sequence (runs after the convolution)
+__global__ void __launch_bounds__(256) mamba_conv_carry_kernel(DlMambaBatch b, const float* __restrict__ in, long long ld, int in_off,
+                                                               float* __restrict__ conv_state, int channels, int taps) {
+    const int n = blockIdx.x;
+    const int last = b.seq_pos0[n] + (b.seq_start[n + 1] - b.seq_start[n]) - 1;
+    for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
+        float v[MB_MAX_TAPS];
+#pragma unroll
+        for (int k = 0; k < MB_MAX_TAPS - 1; ++k)
+            if (k < taps - 1) v[k] = conv_input(b, in, ld, in_off, conv_state, channels, taps, n, last - (taps - 2) + k, ch);
+#pragma unroll
+        for (int k = 0; k < MB_MAX_TAPS - 1; ++k)
+            if (k < taps - 1) conv_state[((size_t)b.seq_slot[n] * (taps - 1) + k) * channels + ch] = v[k];
+    }
+}
+
+extern "C" int dl_mamba_conv(const DlMambaBatch* batch, int M, int n_seq, const float* in, long long ld, int in_off,
+                             const void* w, const void* bias, int wtype, float* conv_state, float* out, int channels,
+                             int taps, void* stream) {
+    if (taps < 1 || taps > MB_MAX_TAPS) { dl_set_error("dl_mamba_conv: 1..%d taps", MB_MAX_TAPS); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    const int gy = (channels + 255) / 256;
+    if (wtype == DL_T_BF16)
+        mamba_conv_kernel<<<dim3(M, gy), 256, 0, st>>>(*batch, in, ld, in_off, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, conv_state, out, channels, taps);
+    else
+        mamba_conv_kernel<<<dim3(M, gy), 256, 0, st>>>(*batch, in, ld, in_off, (const float*)w, (const float*)bias, conv_state, out, channels, taps);
+    LAYER_CHECK_LAUNCH("dl_mamba_conv");
+    if (taps > 1) {
+        mamba_conv_carry_kernel<<<dim3(n_seq, gy), 256, 0, st>>>(*batch, in, ld, in_off, conv_state, channels, taps);
+        LAYER_CHECK_LAUNCH("dl_mamba_conv carry");
+    }
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// the scan: CTA = (sequence, head); thread p owns column p of S (state x vdim) in shared memory
+// ------------------------------------------------------------------------------------------------
+__global__ void mamba_scan_kernel(DlMambaBatch b, DlMambaScanArgs a) {
+    extern __shared__ float sm[];
+    const int n = blockIdx.x, h = blockIdx.y;
+    const int N = a.state, P = a.vdim, H = a.n_heads;
+    const int g = h / (H / a.groups);
+    float* S = sm;                       // [N][P]
+    float* Bs = S + (size_t)N * P;       // [N]
+    float* Cs = Bs + N;                  // [N]
+    const int p = threadIdx.x;
+    const int slot = b.seq_slot[n];
+    float* Sg = a.ssm_state + ((size_t)slot * H + h) * N * P;
+    const bool fresh = b.seq_pos0[n] == 0;
+    if (p < P)
+        for (int i = 0; i < N; ++i) S[i * P + p] = fresh ? 0.f : Sg[i * P + p];
+    const float A = -expf(a.A_log[h]), Dh = a.D[h], dtb = a.dt_bias[h];
+    const int r0 = b.seq_start[n], r1 = b.seq_start[n + 1];
+    const int inner = H * P;
+    for (int r = r0; r < r1; ++r) {
+        const int row = b.seq_rows[r];
+        const float* xbc = a.xbc + (size_t)row * a.ld_xbc;
+        __syncthreads();
+        for (int i = threadIdx.x; i < N; i += blockDim.x) {
+            Bs[i] = xbc[inner + g * N + i];
+            Cs[i] = xbc[inner + a.groups * N + g * N + i];
+        }
+        __syncthreads();
+        if (p < P) {
+            const float dt = softplus_f(a.dt[(size_t)row * a.ld_dt + h] + dtb);
+            const float decay = expf(A * dt);
+            const float x = xbc[h * P + p];
+            const float dx = dt * x;
+            float y = 0.f;
+            for (int i = 0; i < N; ++i) {
+                const float s = fmaf(decay, S[i * P + p], Bs[i] * dx);
+                S[i * P + p] = s;
+                y = fmaf(s, Cs[i], y);
+            }
+            a.y[(size_t)row * a.ld_y + h * P + p] = fmaf(Dh, x, y);
+        }
+    }
+    if (p < P)
+        for (int i = 0; i < N; ++i) Sg[i * P + p] = S[i * P + p];
+}
+
+extern "C" int dl_mamba_scan(const DlMambaBatch* batch, int n_seq, const DlMambaScanArgs* args, void* stream) {
+    const DlMambaScanArgs& a = *args;
+    if (a.n_heads % a.groups != 0) { dl_set_error("dl_mamba_scan: heads must be a multiple of groups"); return -1; }
+    if (a.vdim > 1024) { dl_set_error("dl_mamba_scan: vdim > 1024"); return -1; }
+    const size_t smem = ((size_t)a.state * a.vdim + 2 * (size_t)a.state) * sizeof(float);
+    if (smem > 227 * 1024) { dl_set_error("dl_mamba_scan: state %d x vdim %d does not fit shared memory", a.state, a.vdim); return -1; }
+    cudaError_t e = cudaFuncSetAttribute(mamba_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { dl_set_error("dl_mamba_scan: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
+    const int threads = (a.vdim + 31) / 32 * 32;
+    mamba_scan_kernel<<<dim3(n_seq, a.n_heads), threads, smem, (cudaStream_t)stream>>>(*batch, a);
+    LAYER_CHECK_LAUNCH("dl_mamba_scan");
+    return 0;
+}

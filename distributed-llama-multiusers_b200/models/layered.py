@@ -1,0 +1,458 @@
+"""GPU engine for layer-list models: a model directory (config.json + model.safetensors) whose configuration lists its
+layers one by one, each a token mixer followed by an optional feed-forward, with dense bf16 weights.
+
+    x <- x + post_norm(mixer(pre_norm(x)));   x <- x + post_norm(ff(pre_norm(x)))      per layer, residual in f32
+
+The mixers and feed-forwards are looked up by name (``MIXERS`` / ``FEED_FORWARDS`` below), so another design composes
+the same mechanisms with its own sizes and order; ``ARCHITECTURES`` in models/registry.py maps an architecture name to
+this engine.  Mixers here:
+
+* ``latent_attention`` -- attention whose keys and values are up-projections of one small cached latent per token plus
+  a rotated key part shared by all heads; a layer may read the cache another layer writes (``kv_from``);
+* ``mamba2`` -- a gated selective state-space recurrence with a short causal convolution in front.
+
+What the engine shares with ``LlamaEngine`` is the serving surface (slots, rows with per-row positions, paged token
+cache from ``PageAllocator``, ``forward`` / ``decode_step_greedy`` / ``prefill``), so the scheduler, the batching loop
+and the command line drive it unchanged.  Per sequence slot it owns pages of every latent cache and one row of every
+recurrent layer's state pools; a sequence that starts again at position 0 starts from zeros whatever its slot held.
+
+Numerics: ``dtype="bfloat16"`` keeps weights and caches in bf16 and rounds the activation operand of every matrix
+product to bf16 (f32 accumulation); norms, softmax, rotary angles, the residual stream, the recurrence with its decays
+and step sizes are f32.  ``dtype="float32"`` widens weights and caches to f32 and rounds nothing.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..formats.safetensors import SafetensorsFile
+from .paging import PAGE, PageAllocator
+
+
+# --------------------------------------------------------------------------------------------------
+# configuration
+# --------------------------------------------------------------------------------------------------
+@dataclass
+class LayerSpec:
+    type: str
+    mixer: dict
+    mlp: Optional[dict]
+
+
+@dataclass
+class LayerListConfig:
+    architecture: str
+    width: int
+    vocab: int
+    norm_eps: float
+    logit_softcap: float
+    layers: List[LayerSpec] = field(default_factory=list)
+    seq_len: int = 0
+
+    # the serving code reads these names from every engine's header
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def n_layers(self) -> int:
+        return len(self.layers)
+
+    @staticmethod
+    def from_dict(c: dict) -> "LayerListConfig":
+        layers = [LayerSpec(l["type"], dict(l["mixer"]), dict(l["mlp"]) if l.get("mlp") else None) for l in c["layers"]]
+        return LayerListConfig(architecture=c["architecture"], width=int(c["width"]), vocab=int(c["vocab"]),
+                               norm_eps=float(c["norm"]["eps"]), logit_softcap=float(c.get("logit_softcap") or 0.0),
+                               layers=layers)
+
+    @staticmethod
+    def load(model_dir: str) -> "LayerListConfig":
+        with open(os.path.join(model_dir, "config.json")) as f:
+            return LayerListConfig.from_dict(json.load(f))
+
+    def describe(self) -> str:
+        kinds = ", ".join(f"{sum(1 for l in self.layers if l.type == t)} x {t}" for t in sorted({l.type for l in self.layers}))
+        return (f"💡 Arch: {self.architecture}\n💡 Width: {self.width}\n💡 VocabSize: {self.vocab}\n"
+                f"💡 nLayers: {len(self.layers)} ({kinds})\n💡 SeqLen: {self.seq_len}")
+
+
+def rotary_frequencies(base: float, dims: int) -> torch.Tensor:
+    """f_i = base^(-2 i / dims), i < dims / 2, in f64 (the kernels form pos * f_i in f64)."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+
+
+# --------------------------------------------------------------------------------------------------
+# mixers
+# --------------------------------------------------------------------------------------------------
+class LatentAttentionMixer:
+    """Tensors <prefix>dq, dq.norm, uq, [dkv, dkv.norm], uk, uv, g, o.  Sizes from the layer's mixer entry: heads, dim
+    (unrotated query / key dims per head), rot_dim (rotated dims per head, one shared key part), vdim, q_rank, kv_rank,
+    scale, rot {base, dims}, and kv_from (index of the layer whose cache this one reads)."""
+
+    def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
+        self.eng, self.index = eng, index
+        self.H, self.dn, self.dr, self.dv = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
+        self.q_rank, self.rank = int(m["q_rank"]), int(m["kv_rank"])
+        self.scale = float(m["scale"])
+        self.rope_dims = int(m["rot"]["dims"])
+        if self.rope_dims > self.dr or self.rope_dims % 2:
+            raise ValueError(f"layer {index}: rotary dims {self.rope_dims} do not fit rot_dim {self.dr}")
+        self.freqs = rotary_frequencies(float(m["rot"]["base"]), self.rope_dims).to(eng.device)
+        self.kv_from = m.get("kv_from")
+        W, V = eng.weight, eng.vector
+        self.w_dq, self.dq_norm, self.w_uq = W(prefix + "dq"), V(prefix + "dq.norm"), W(prefix + "uq")
+        self.w_g, self.w_o = W(prefix + "g"), W(prefix + "o")
+        H, dn, dv, r = self.H, self.dn, self.dv, self.rank
+        # key up-projection per head, transposed, so that  q_lat[h] = U_k,h^T q_h  is a product against rows of K = dn
+        self.w_uk_t = W(prefix + "uk").reshape(H, dn, r).transpose(1, 2).contiguous()
+        self.w_uv = W(prefix + "uv").reshape(H, dv, r).contiguous()
+        if self.kv_from is None:
+            self.w_dkv, self.dkv_norm = W(prefix + "dkv"), V(prefix + "dkv.norm")
+            self.cache = torch.zeros(eng.n_pages, PAGE, r + self.dr, dtype=eng.wdtype, device=eng.device)
+        else:
+            self.cache = None                      # bound to the owner's cache once all layers exist
+
+    def scratch(self) -> Dict[str, int]:
+        H = self.H
+        return {"cq": self.q_rank, "q": H * (self.dn + self.dr), "kv": self.rank + self.dr, "q_lat": H * self.rank,
+                "o_lat": H * self.rank, "o": H * self.dv, "og": H * self.dv}
+
+    def bind(self, mixers: list):
+        if self.kv_from is not None:
+            src = mixers[int(self.kv_from)]
+            if not isinstance(src, LatentAttentionMixer) or src.kv_from is not None:
+                raise ValueError(f"layer {self.index}: kv_from {self.kv_from} is not a layer with a cache of its own")
+            if (src.rank, src.dr, src.rope_dims) != (self.rank, self.dr, self.rope_dims):
+                raise ValueError(f"layer {self.index}: cache shape differs from layer {self.kv_from}")
+            self.cache = src.cache
+
+    def weight_bytes(self) -> int:
+        ts = [self.w_dq, self.w_uq, self.w_g, self.w_o, self.w_uk_t, self.w_uv] + ([self.w_dkv] if self.kv_from is None else [])
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
+        e, L, rx = self.eng, self.eng.L, self.eng.round_x
+        H, dn, dr, dv, r = self.H, self.dn, self.dr, self.dv, self.rank
+        cq, q, o, og = (e.buf(n) for n in ("cq", "q", "o", "og"))
+        q_lat, o_lat = e.buf("q_lat", H * r), e.buf("o_lat", H * r)          # read as [M][H][rank], no row padding
+        hd = dn + dr
+        L.dense(self.w_dq, h, cq, M, rx)
+        L.rms_norm(cq, cq, M, self.q_rank, e.cfg.norm_eps, w=self.dq_norm)
+        L.dense(self.w_uq, cq, q, M, rx)
+        L.rope_rows(q, M, H, hd, dn, self.rope_dims, self.freqs, e.pos)
+        if self.kv_from is None:
+            kv = e.buf("kv")
+            L.dense(self.w_dkv, h, kv, M, rx)
+            L.latent_kv_write(kv, M, self.dkv_norm, e.cfg.norm_eps, r, dr, self.rope_dims, self.freqs, e.pos, e.slot,
+                              e.block_table, self.cache)
+        L.dense_heads(self.w_uk_t, q, q_lat, M, rx, hd, r)
+        L.latent_attention(q_lat, q, hd, dn, o_lat, M, H, r, dr, self.scale, e.pos, e.slot, e.block_table, self.cache)
+        L.dense_heads(self.w_uv, o_lat, o, M, rx, r, dv)
+        L.dense(self.w_g, h, og, M, rx, epi=L.DENSE_SIGMOID_MUL, aux=o)
+        L.dense(self.w_o, og, y, M, rx)
+
+
+class Mamba2Mixer:
+    """Tensors <prefix>in, conv, conv.b, dt_bias, A_log, D, norm, o.  Sizes: heads, vdim (inner = heads * vdim), state,
+    groups (heads per B / C group = heads / groups), conv (taps), norm_groups."""
+
+    def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
+        self.eng, self.index = eng, index
+        self.H, self.P, self.N, self.G = int(m["heads"]), int(m["vdim"]), int(m["state"]), int(m["groups"])
+        self.taps, self.norm_groups = int(m["conv"]), int(m["norm_groups"])
+        self.inner = self.H * self.P
+        self.channels = self.inner + 2 * self.G * self.N
+        if self.H % self.G or self.inner % self.norm_groups:
+            raise ValueError(f"layer {index}: heads / groups / norm_groups do not divide")
+        W, V = eng.weight, eng.vector
+        self.w_in, self.w_o = W(prefix + "in"), W(prefix + "o")
+        self.w_conv, self.b_conv = W(prefix + "conv"), W(prefix + "conv.b")
+        self.dt_bias, self.A_log, self.D, self.norm = (V(prefix + n) for n in ("dt_bias", "A_log", "D", "norm"))
+        if tuple(self.w_in.shape) != (2 * self.inner + 2 * self.G * self.N + self.H, eng.cfg.width):
+            raise ValueError(f"layer {index}: input projection has shape {tuple(self.w_in.shape)}")
+        # the slot's recurrent state: S [heads][state][vdim] and the last taps-1 convolution inputs, both f32
+        self.ssm_state = torch.zeros(eng.n_slots, self.H, self.N, self.P, dtype=torch.float32, device=eng.device)
+        self.conv_state = torch.zeros(eng.n_slots, max(1, self.taps - 1), self.channels, dtype=torch.float32, device=eng.device)
+
+    def scratch(self) -> Dict[str, int]:
+        return {"zx": 2 * self.inner + 2 * self.G * self.N + self.H, "xbc": self.channels, "ys": self.inner, "yn": self.inner}
+
+    def bind(self, mixers: list):
+        pass
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w_conv))
+
+    def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
+        e, L, rx = self.eng, self.eng.L, self.eng.round_x
+        zx, ys, yn = e.buf("zx"), e.buf("ys"), e.buf("yn")
+        xbc = e.buf("xbc", self.channels)
+        L.dense(self.w_in, h, zx, M, rx)
+        L.mamba_conv(e.mamba_batch, M, e.n_seq, zx, self.inner, self.w_conv, self.b_conv, self.conv_state, xbc)
+        dt = zx[:, 2 * self.inner + 2 * self.G * self.N:]
+        L.mamba_scan(e.mamba_batch, e.n_seq, xbc, dt, self.dt_bias, self.A_log, self.D, ys, self.ssm_state, self.H, self.P,
+                     self.N, self.G)
+        L.rms_norm(ys, yn, M, self.inner, e.cfg.norm_eps, w=self.norm, groups=self.norm_groups, gate=zx)
+        L.dense(self.w_o, yn, y, M, rx)
+
+
+class DenseFeedForward:
+    """Tensors <prefix>up, down:  W_down relu(W_up h)^2."""
+
+    def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
+        self.eng = eng
+        self.ff = int(m["ff"])
+        self.w_up, self.w_down = eng.weight(prefix + "up"), eng.weight(prefix + "down")
+
+    def scratch(self) -> Dict[str, int]:
+        return {"up": self.ff}
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
+        e, L = self.eng, self.eng.L
+        up = e.buf("up")
+        L.dense(self.w_up, h, up, M, e.round_x, epi=L.DENSE_RELU2)
+        L.dense(self.w_down, up, y, M, e.round_x)
+
+
+MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer}
+FEED_FORWARDS = {"dense": DenseFeedForward}
+
+
+class _Layer:
+    def __init__(self, eng: "LayerListEngine", i: int, spec: LayerSpec):
+        p = f"l{i}."
+        if spec.type not in MIXERS:
+            raise ValueError(f"layer {i}: unknown mixer type {spec.type!r}")
+        self.mixer = MIXERS[spec.type](eng, i, spec.mixer, p + "mix.")
+        self.norm1, self.norm1b = eng.vector(p + "norm1"), eng.vector(p + "norm1b")
+        self.ff = None
+        if spec.mlp is not None:
+            kind = spec.mlp.get("kind", "dense")
+            if kind not in FEED_FORWARDS:
+                raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
+            self.ff = FEED_FORWARDS[kind](eng, i, spec.mlp, p + "mlp.")
+            self.norm2, self.norm2b = eng.vector(p + "norm2"), eng.vector(p + "norm2b")
+
+
+# --------------------------------------------------------------------------------------------------
+# the engine
+# --------------------------------------------------------------------------------------------------
+class LayerListEngine:
+    def __init__(self, model_path: str, rank: int = 0, world: int = 1, group=None, max_rows: int = 32, n_slots: int = 4,
+                 max_seq_len: int = 2048, dtype: str = "bfloat16", n_pages: Optional[int] = None,
+                 device: Optional[torch.device] = None, **_unused):
+        if world != 1:
+            raise NotImplementedError("layer-list models run on one GPU (no tensor-parallel slicing of their mixers yet)")
+        if dtype not in ("bfloat16", "float32"):
+            raise ValueError(f"dtype {dtype!r}: bfloat16 or float32")
+        from ..ops import layers as L            # fails loudly if the CUDA library is missing
+        L.layers_lib()
+        self.L = L
+        self.cfg = self.h = LayerListConfig.load(model_path)
+        self.rank, self.world, self.group = 0, 1, None
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.dtype = dtype
+        self.wdtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        self.round_x = dtype == "bfloat16"
+        self.max_rows, self.n_slots = int(max_rows), int(n_slots)
+        self.seq_len = self.cfg.seq_len = int(max_seq_len)
+        self.max_pages = (self.seq_len + PAGE - 1) // PAGE
+        self.n_pages = int(n_pages) if n_pages else self.n_slots * self.max_pages
+        self.pages = PageAllocator(self.n_pages, self.n_slots, self.max_pages)
+        self._slot_len = np.zeros(self.n_slots, dtype=np.int64)       # tokens each slot has been fed (the state's position)
+        dev, R = self.device, self.max_rows
+        self._st = SafetensorsFile(os.path.join(model_path, "model.safetensors"))
+        try:
+            self.embed = self.weight("embed")
+            if tuple(self.embed.shape) != (self.cfg.vocab, self.cfg.width):
+                raise ValueError(f"embed has shape {tuple(self.embed.shape)}")
+            self.layers = [_Layer(self, i, spec) for i, spec in enumerate(self.cfg.layers)]
+            self.final_norm, self.head = self.vector("final.norm"), self.weight("head")
+        finally:
+            self._st.close()
+        mixers = [l.mixer for l in self.layers]
+        for mx in mixers:
+            mx.bind(mixers)
+        # scratch: one f32 buffer per name, as wide as the widest user
+        widths: Dict[str, int] = {}
+        for l in self.layers:
+            for part in (l.mixer, l.ff):
+                if part is not None:
+                    for name, w in part.scratch().items():
+                        widths[name] = max(widths.get(name, 0), w)
+        self._bufs = {n: torch.zeros(R * w, dtype=torch.float32, device=dev) for n, w in widths.items()}
+        self._widths = widths
+        self.x = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
+        self.hn = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
+        self.y = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
+        self.logits = torch.zeros(R, self.cfg.vocab, dtype=torch.float32, device=dev)
+        self.out_tokens = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.h_out_tokens = torch.zeros(R, dtype=torch.int32).pin_memory()
+        # batch descriptor (one pinned -> device copy per step):
+        #   tokens | pos | slot | row_seq | seq_rows | logit_rows   [R] each, then seq_start [S+1] | seq_slot [S] | seq_pos0 [S]
+        S = self.n_slots
+        self._desc_len = 6 * R + 3 * S + 1
+        self.h_desc = torch.zeros(self._desc_len, dtype=torch.int32).pin_memory()
+        self.desc = torch.zeros(self._desc_len, dtype=torch.int32, device=dev)
+        d = self.desc
+        self.tokens, self.pos, self.slot, self.row_seq, self.seq_rows, self.logit_rows = (d[i * R:(i + 1) * R] for i in range(6))
+        o = 6 * R
+        self.seq_start, self.seq_slot, self.seq_pos0 = d[o:o + S + 1], d[o + S + 1:o + 2 * S + 1], d[o + 2 * S + 1:o + 3 * S + 1]
+        self.mamba_batch = L.mamba_batch(self.pos, self.row_seq, self.seq_start, self.seq_rows, self.seq_slot, self.seq_pos0)
+        self.n_seq = 0
+        self.block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32, device=dev)
+        self.h_block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32).pin_memory()
+        self._staging_ev: Optional[torch.cuda.Event] = None
+        self.layer_probe = None              # a list: forward() appends a copy of the residual stream after every layer
+        torch.cuda.synchronize()
+
+    # ---- weights ---------------------------------------------------------------------------------
+    def weight(self, name: str) -> torch.Tensor:
+        """A matrix (or a convolution's taps and bias) in the engine's weight type."""
+        if name not in self._st:
+            raise KeyError(f"model.safetensors has no tensor {name!r}")
+        return self._st.tensor(name).to(self.wdtype).to(self.device).contiguous()
+
+    def vector(self, name: str) -> torch.Tensor:
+        """A norm weight or a per-head constant: always f32 on the device."""
+        if name not in self._st:
+            raise KeyError(f"model.safetensors has no tensor {name!r}")
+        return self._st.tensor(name).to(torch.float32).to(self.device).contiguous()
+
+    def buf(self, name: str, width: Optional[int] = None) -> torch.Tensor:
+        """Scratch `name` as [max_rows][width] (default: the width it was sized for)."""
+        w = width or self._widths[name]
+        return self._bufs[name][:self.max_rows * w].view(self.max_rows, w)
+
+    def weight_bytes(self) -> int:
+        n = sum(l.mixer.weight_bytes() + (l.ff.weight_bytes() if l.ff else 0) for l in self.layers)
+        return n + self.head.numel() * self.head.element_size()
+
+    # ---- slots / pages ---------------------------------------------------------------------------
+    def usable_pages(self) -> int:
+        return self.n_pages
+
+    def alloc_slot(self) -> int:
+        s = self.pages.alloc_slot()
+        self._slot_len[s] = 0
+        return s
+
+    def free_slot(self, slot: int):
+        self.pages.free_slot(slot)
+        self._slot_len[slot] = 0
+
+    def ensure_capacity(self, slot: int, n_tokens: int):
+        self.pages.ensure(slot, n_tokens)
+
+    # ---- one step ----------------------------------------------------------------------------------
+    def set_batch(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int],
+                  logit_rows: Sequence[int]) -> int:
+        M, R, S = len(tokens), self.max_rows, self.n_slots
+        if not 1 <= M <= R:
+            raise ValueError(f"{M} rows in a batch of an engine built for {R}")
+        by_slot: Dict[int, List[int]] = {}
+        for m, s in enumerate(slots):
+            by_slot.setdefault(int(s), []).append(m)
+        if len(by_slot) > S:
+            raise ValueError("more sequences in a batch than slots")
+        if self._staging_ev is not None:
+            self._staging_ev.synchronize()
+        hd = self.h_desc.numpy()
+        hd[0:M], hd[R:R + M], hd[2 * R:2 * R + M] = tokens, positions, slots
+        o, at = 6 * R, 0
+        for n, (s, rows) in enumerate(by_slot.items()):
+            p0 = int(positions[rows[0]])
+            for i, m in enumerate(rows):
+                if int(positions[m]) != p0 + i:
+                    raise ValueError(f"slot {s}: rows of a sequence must hold consecutive positions in order")
+            # a recurrent state cannot be rewound: a sequence goes on where it stopped, or starts again at 0
+            if p0 != 0 and p0 != int(self._slot_len[s]):
+                raise ValueError(f"slot {s}: position {p0} does not continue the sequence (its state is at {int(self._slot_len[s])})")
+            hd[3 * R + np.asarray(rows)] = n
+            hd[4 * R + at:4 * R + at + len(rows)] = rows
+            hd[o + n] = at
+            hd[o + S + 1 + n] = s
+            hd[o + 2 * S + 1 + n] = p0
+            at += len(rows)
+            self.pages.ensure(s, p0 + len(rows))
+            self._slot_len[s] = p0 + len(rows)
+        hd[o + len(by_slot)] = at
+        nl = len(logit_rows)
+        hd[5 * R:5 * R + nl] = logit_rows
+        if self.pages.dirty:
+            self.h_block_table.numpy()[:] = self.pages.table
+            self.block_table.copy_(self.h_block_table, non_blocking=True)
+            self.pages.dirty = False
+        self.desc.copy_(self.h_desc, non_blocking=True)
+        if self._staging_ev is None:
+            self._staging_ev = torch.cuda.Event()
+        self._staging_ev.record()
+        self.n_seq = len(by_slot)
+        return M
+
+    def _launch_forward(self, M: int, n_logits: int):
+        L, cfg, eps = self.L, self.cfg, self.cfg.norm_eps
+        x, hn, y, W = self.x, self.hn, self.y, self.cfg.width
+        L.embed_rows(self.embed, self.tokens, x, M)
+        for l in self.layers:
+            L.rms_norm(x, hn, M, W, eps, w=l.norm1, plus_one=True)
+            l.mixer.forward(hn, y, M)
+            L.rms_norm(y, x, M, W, eps, w=l.norm1b, plus_one=True, accumulate=True)
+            if l.ff is not None:
+                L.rms_norm(x, hn, M, W, eps, w=l.norm2, plus_one=True)
+                l.ff.forward(hn, y, M)
+                L.rms_norm(y, x, M, W, eps, w=l.norm2b, plus_one=True, accumulate=True)
+            if self.layer_probe is not None:
+                self.layer_probe.append(x[:M].clone())
+        if n_logits:
+            L.rms_norm(x, hn, n_logits, W, eps, w=self.final_norm, plus_one=True, rows=self.logit_rows)
+            if cfg.logit_softcap > 0:
+                L.dense(self.head, hn, self.logits, n_logits, self.round_x, epi=L.DENSE_SOFTCAP, param=cfg.logit_softcap)
+            else:
+                L.dense(self.head, hn, self.logits, n_logits, self.round_x)
+
+    @torch.no_grad()
+    def forward(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int], logits_from: int = 0,
+                greedy: bool = False, logit_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """One forward over a batch of rows: any mix of prompt portions and single decoded tokens; rows of one sequence
+        hold consecutive positions in order.  Returns the device logits [n][vocab] of rows logits_from.. (or of
+        `logit_rows`, any rows in any order), valid until the next forward."""
+        rows = list(logit_rows) if logit_rows is not None else list(range(logits_from, len(tokens)))
+        M = self.set_batch(tokens, positions, slots, rows)
+        self._launch_forward(M, len(rows))
+        if greedy and rows:
+            self.L.argmax(self.logits, len(rows), self.out_tokens)
+        return self.logits[:len(rows)]
+
+    def prefill(self, slot: int, tokens: Sequence[int], start_pos: int = 0, chunk: Optional[int] = None):
+        """Evaluate a prompt in portions of <= max_rows rows; returns the logits of the last token."""
+        chunk = chunk or self.max_rows
+        out = None
+        for i in range(0, len(tokens), chunk):
+            part = list(tokens[i:i + chunk])
+            pos = list(range(start_pos + i, start_pos + i + len(part)))
+            out = self.forward(part, pos, [slot] * len(part), logits_from=len(part) - 1)
+        return out
+
+    def decode_step_greedy(self, tokens, positions, slots, logits_from: int = 0) -> List[int]:
+        n = len(tokens) - logits_from
+        self.forward(tokens, positions, slots, logits_from, greedy=True)
+        self.h_out_tokens.copy_(self.out_tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_out_tokens[:n].tolist()
+
+    def decode_greedy_host(self, tokens, positions, slots) -> List[int]:
+        return self.decode_step_greedy(tokens, positions, slots, 0)
+
+    def close(self):
+        torch.cuda.synchronize()

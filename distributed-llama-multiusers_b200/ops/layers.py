@@ -1,0 +1,174 @@
+"""Torch-tensor wrappers over the layer-list model kernels (libdllama_b200_layers.so; C ABI in include/dllama_b200.h).
+
+One function per kernel launch, all on ``torch.cuda.current_stream()``; nothing here allocates.  Activations are f32
+tensors; weights are bf16 or f32 tensors (``wtype`` follows the tensor's dtype), caches likewise.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import lib
+from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
+                  DlLatentAttnArgs, DlLatentKvArgs, DlMambaBatch, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
+
+PAGE_SIZE = 32
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _type(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return T_BF16
+    if t.dtype == torch.float32:
+        return T_F32
+    raise TypeError(f"layer kernels take bf16 or f32 weights and caches, not {t.dtype}")
+
+
+def sm_count() -> int:
+    return int(layers_lib().dl_device_sm_count())
+
+
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, M: int):
+    check_layers(layers_lib().dl_embed_rows(table.data_ptr(), _type(table), tokens.data_ptr(), x.data_ptr(), M,
+                                            table.shape[1], _stream()), "dl_embed_rows")
+    lib.count_launch()
+
+
+def dense(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor, M: int, round_x: bool, epi: int = DENSE_STORE,
+          aux: Optional[torch.Tensor] = None, param: float = 0.0):
+    """y[:M] = epi(x[:M] @ w^T); w [N][K] (rows may be strided), x [.., >= K] and y [.., >= N] row-major f32."""
+    N, K = w.shape
+    a = DlDenseArgs()
+    a.W, a.wtype, a.ldw, a.w_bs = w.data_ptr(), _type(w), w.stride(0), 0
+    a.X, a.ldx, a.x_bs = x.data_ptr(), x.stride(0), 0
+    a.Y, a.ldy, a.y_bs = y.data_ptr(), y.stride(0), 0
+    a.M, a.N, a.K, a.batch = M, N, K, 1
+    a.round_x, a.epi = 1 if round_x else 0, epi
+    a.aux, a.ld_aux, a.aux_bs = _p(aux), (aux.stride(0) if aux is not None else 0), 0
+    a.param = param
+    check_layers(layers_lib().dl_dense(a, _stream()), "dl_dense")
+    lib.count_launch()
+
+
+def dense_heads(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor, M: int, round_x: bool, x_head_stride: int,
+                y_head_stride: int):
+    """Per-head products in one launch: y[m, h*ys : h*ys + N] = x[m, h*xs : h*xs + K] @ w[h]^T for w [H][N][K]."""
+    H, N, K = w.shape
+    a = DlDenseArgs()
+    a.W, a.wtype, a.ldw, a.w_bs = w.data_ptr(), _type(w), w.stride(1), w.stride(0)
+    a.X, a.ldx, a.x_bs = x.data_ptr(), x.stride(0), x_head_stride
+    a.Y, a.ldy, a.y_bs = y.data_ptr(), y.stride(0), y_head_stride
+    a.M, a.N, a.K, a.batch = M, N, K, H
+    a.round_x, a.epi = 1 if round_x else 0, DENSE_STORE
+    a.aux, a.ld_aux, a.aux_bs, a.param = None, 0, 0, 0.0
+    check_layers(layers_lib().dl_dense(a, _stream()), "dl_dense")
+    lib.count_launch()
+
+
+def rms_norm(x: torch.Tensor, y: torch.Tensor, M: int, dim: int, eps: float, w: Optional[torch.Tensor] = None,
+             plus_one: bool = False, groups: int = 1, gate: Optional[torch.Tensor] = None, accumulate: bool = False,
+             rows: Optional[torch.Tensor] = None):
+    a = DlNormArgs()
+    a.x, a.ldx = x.data_ptr(), x.stride(0)
+    a.gate, a.ld_gate = _p(gate), (gate.stride(0) if gate is not None else 0)
+    a.w, a.y, a.ldy, a.rows = _p(w), y.data_ptr(), y.stride(0), _p(rows)
+    a.M, a.dim, a.groups, a.eps = M, dim, groups, eps
+    a.plus_one, a.accumulate = 1 if plus_one else 0, 1 if accumulate else 0
+    check_layers(layers_lib().dl_rms_norm(a, _stream()), "dl_rms_norm")
+    lib.count_launch()
+
+
+def latent_kv_write(kv: torch.Tensor, M: int, norm_w: torch.Tensor, eps: float, rank: int, rot: int, rope_dims: int,
+                    freqs: torch.Tensor, pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
+    a = DlLatentKvArgs()
+    a.kv, a.ld, a.norm_w, a.eps = kv.data_ptr(), kv.stride(0), norm_w.data_ptr(), eps
+    a.rank, a.rot, a.rope_dims, a.freqs = rank, rot, rope_dims, freqs.data_ptr()
+    a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
+    a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
+    a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    check_layers(layers_lib().dl_latent_kv_write(a, M, _stream()), "dl_latent_kv_write")
+    lib.count_launch()
+
+
+def rope_rows(x: torch.Tensor, M: int, n_heads: int, head_stride: int, offset: int, rope_dims: int, freqs: torch.Tensor,
+              pos: torch.Tensor):
+    check_layers(layers_lib().dl_rope_rows(x.data_ptr(), x.stride(0), M, n_heads, head_stride, offset, rope_dims,
+                                           freqs.data_ptr(), pos.data_ptr(), _stream()), "dl_rope_rows")
+    lib.count_launch()
+
+
+def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_head_stride: int, q_rot_offset: int, out: torch.Tensor,
+                     M: int, n_heads: int, rank: int, rot: int, scale: float, pos, slot, block_table: torch.Tensor,
+                     cache: torch.Tensor):
+    a = DlLatentAttnArgs()
+    a.q_lat, a.q, a.ldq = q_lat.data_ptr(), q.data_ptr(), q.stride(0)
+    a.q_head_stride, a.q_rot_offset, a.out = q_head_stride, q_rot_offset, out.data_ptr()
+    a.n_heads, a.rank, a.rot, a.scale = n_heads, rank, rot, scale
+    a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
+    a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
+    a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    check_layers(layers_lib().dl_latent_attention(a, M, _stream()), "dl_latent_attention")
+    lib.count_launch()
+
+
+def mamba_batch(pos, row_seq, seq_start, seq_rows, seq_slot, seq_pos0) -> DlMambaBatch:
+    b = DlMambaBatch()
+    b.pos, b.row_seq, b.seq_start = pos.data_ptr(), row_seq.data_ptr(), seq_start.data_ptr()
+    b.seq_rows, b.seq_slot, b.seq_pos0 = seq_rows.data_ptr(), seq_slot.data_ptr(), seq_pos0.data_ptr()
+    return b
+
+
+def mamba_conv(batch: DlMambaBatch, M: int, n_seq: int, zx: torch.Tensor, in_off: int, w: torch.Tensor,
+               bias: torch.Tensor, conv_state: torch.Tensor, out: torch.Tensor):
+    channels, taps = w.shape
+    assert bias.dtype == w.dtype and out.stride(0) == channels
+    check_layers(layers_lib().dl_mamba_conv(batch, M, n_seq, zx.data_ptr(), zx.stride(0), in_off, w.data_ptr(),
+                                            bias.data_ptr(), _type(w), conv_state.data_ptr(), out.data_ptr(), channels,
+                                            taps, _stream()), "dl_mamba_conv")
+    lib.count_launch(2 if taps > 1 else 1)
+
+
+def mamba_scan(batch: DlMambaBatch, n_seq: int, xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A_log, D, y: torch.Tensor,
+               ssm_state: torch.Tensor, n_heads: int, vdim: int, state: int, groups: int):
+    """dt: a view whose element [m, h] is the raw step size of head h of row m."""
+    a = DlMambaScanArgs()
+    a.xbc, a.ld_xbc, a.dt, a.ld_dt = xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0)
+    a.dt_bias, a.A_log, a.D = dt_bias.data_ptr(), A_log.data_ptr(), D.data_ptr()
+    a.y, a.ld_y, a.ssm_state = y.data_ptr(), y.stride(0), ssm_state.data_ptr()
+    a.n_heads, a.vdim, a.state, a.groups = n_heads, vdim, state, groups
+    check_layers(layers_lib().dl_mamba_scan(batch, n_seq, a, _stream()), "dl_mamba_scan")
+    lib.count_launch()
+
+
+_ARGMAX_SCRATCH = {}
+
+
+def argmax(logits: torch.Tensor, M: int, out: torch.Tensor):
+    """out[m] = argmax(logits[m]) for the first M rows (the multi-CTA pick shared with the other engines)."""
+    L = layers_lib()
+    key = str(out.device)
+    sc = _ARGMAX_SCRATCH.get(key)
+    if sc is None:
+        sc = _ARGMAX_SCRATCH[key] = torch.zeros(int(L.dl_argmax_scratch_bytes(256)), dtype=torch.uint8, device=out.device)
+    vocab = logits.shape[1]
+    for m0 in range(0, M, 256):
+        n = min(256, M - m0)
+        check_layers(L.dl_argmax(logits[m0:].data_ptr(), n, vocab, logits.stride(0), out[m0:].data_ptr(), None, 0, None, 0, 0,
+                                 None, None, 0, sc.data_ptr(), 0, _stream()), "dl_argmax")
+        lib.count_launch()
+
+
+def sample_rows(logits: torch.Tensor, temperature, topp, coin, tokens_out):
+    M, vocab = logits.shape
+    check_layers(layers_lib().dl_sample_rows(logits.data_ptr(), M, vocab, logits.stride(0), temperature.data_ptr(),
+                                             topp.data_ptr(), coin.data_ptr(), tokens_out.data_ptr(), _stream()),
+                 "dl_sample_rows")
+    lib.count_launch()

@@ -11,6 +11,7 @@ import os
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CUDA_LIB_PATH = os.path.join(_PKG, "lib", "libdllama_b200_cuda.so")
 HOST_LIB_PATH = os.path.join(_PKG, "lib", "libdllama_b200_host.so")
+LAYERS_LIB_PATH = os.path.join(_PKG, "lib", "libdllama_b200_layers.so")
 
 DL_MAX_PEERS = 8
 EPI_STORE, EPI_QKV_ROPE, EPI_SILU_MUL = 0, 1, 2
@@ -202,6 +203,101 @@ def cuda_lib():
 def check(rc: int, what: str = ""):
     if rc != 0:
         msg = cuda_lib().dl_last_error().decode("utf-8", "replace")
+        raise NativeLibraryError(f"{what} failed ({rc}): {msg}")
+
+
+# ---- libdllama_b200_layers.so: kernels of layer-list models (dense weights, latent attention, Mamba-2) --------------
+T_F32, T_BF16 = 0, 1
+DENSE_STORE, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP = 0, 1, 2, 3
+
+
+class DlDenseArgs(C.Structure):
+    """Mirror of ``DlDenseArgs`` in include/dllama_b200.h."""
+    _fields_ = [("W", C.c_void_p), ("wtype", C.c_int), ("ldw", C.c_longlong), ("w_bs", C.c_longlong),
+                ("X", C.c_void_p), ("ldx", C.c_longlong), ("x_bs", C.c_longlong),
+                ("Y", C.c_void_p), ("ldy", C.c_longlong), ("y_bs", C.c_longlong),
+                ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("batch", C.c_int),
+                ("round_x", C.c_int), ("epi", C.c_int),
+                ("aux", C.c_void_p), ("ld_aux", C.c_longlong), ("aux_bs", C.c_longlong),
+                ("param", C.c_float)]
+
+
+class DlNormArgs(C.Structure):
+    """Mirror of ``DlNormArgs``."""
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_longlong), ("gate", C.c_void_p), ("ld_gate", C.c_longlong),
+                ("w", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong), ("rows", C.c_void_p),
+                ("M", C.c_int), ("dim", C.c_int), ("groups", C.c_int), ("eps", C.c_float),
+                ("plus_one", C.c_int), ("accumulate", C.c_int)]
+
+
+class DlLatentKvArgs(C.Structure):
+    """Mirror of ``DlLatentKvArgs``."""
+    _fields_ = [("kv", C.c_void_p), ("ld", C.c_longlong), ("norm_w", C.c_void_p), ("eps", C.c_float),
+                ("rank", C.c_int), ("rot", C.c_int), ("rope_dims", C.c_int), ("freqs", C.c_void_p),
+                ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
+                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
+
+
+class DlLatentAttnArgs(C.Structure):
+    """Mirror of ``DlLatentAttnArgs``."""
+    _fields_ = [("q_lat", C.c_void_p), ("q", C.c_void_p), ("ldq", C.c_longlong), ("q_head_stride", C.c_int),
+                ("q_rot_offset", C.c_int), ("out", C.c_void_p), ("n_heads", C.c_int), ("rank", C.c_int),
+                ("rot", C.c_int), ("scale", C.c_float), ("pos", C.c_void_p), ("slot", C.c_void_p),
+                ("block_table", C.c_void_p), ("max_pages", C.c_int), ("page_size", C.c_int),
+                ("cache", C.c_void_p), ("ctype", C.c_int)]
+
+
+class DlMambaBatch(C.Structure):
+    """Mirror of ``DlMambaBatch``."""
+    _fields_ = [("pos", C.c_void_p), ("row_seq", C.c_void_p), ("seq_start", C.c_void_p), ("seq_rows", C.c_void_p),
+                ("seq_slot", C.c_void_p), ("seq_pos0", C.c_void_p)]
+
+
+class DlMambaScanArgs(C.Structure):
+    """Mirror of ``DlMambaScanArgs``."""
+    _fields_ = [("xbc", C.c_void_p), ("ld_xbc", C.c_longlong), ("dt", C.c_void_p), ("ld_dt", C.c_longlong),
+                ("dt_bias", C.c_void_p), ("A_log", C.c_void_p), ("D", C.c_void_p),
+                ("y", C.c_void_p), ("ld_y", C.c_longlong), ("ssm_state", C.c_void_p),
+                ("n_heads", C.c_int), ("vdim", C.c_int), ("state", C.c_int), ("groups", C.c_int)]
+
+
+_layers = None
+
+
+def layers_lib():
+    """Load (once) and return the layer-list model library with argtypes set."""
+    global _layers
+    if _layers is not None:
+        return _layers
+    if not os.path.exists(LAYERS_LIB_PATH):
+        raise NativeLibraryError(
+            f"{LAYERS_LIB_PATH} is missing: run `python build.py layers` (nvcc, sm_100a) before using GPU ops")
+    L = C.CDLL(LAYERS_LIB_PATH)
+    vp, i32, i64, u32 = C.c_void_p, C.c_int, C.c_longlong, C.c_uint32
+    L.dl_last_error.restype = C.c_char_p
+    L.dl_device_sm_count.restype = i32
+    L.dl_dense.argtypes = [C.POINTER(DlDenseArgs), vp]
+    L.dl_embed_rows.argtypes = [vp, i32, vp, vp, i32, i32, vp]
+    L.dl_rms_norm.argtypes = [C.POINTER(DlNormArgs), vp]
+    L.dl_latent_kv_write.argtypes = [C.POINTER(DlLatentKvArgs), i32, vp]
+    L.dl_rope_rows.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
+    L.dl_latent_attention.argtypes = [C.POINTER(DlLatentAttnArgs), i32, vp]
+    L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
+    L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
+    L.dl_sample_rows.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
+    L.dl_argmax.argtypes = [vp, i32, i32, i32, vp, vp, i32, vp, u32, u32, vp, vp, i32, vp, i32, vp]
+    L.dl_argmax_scratch_bytes.restype = i64
+    L.dl_argmax_scratch_bytes.argtypes = [i32]
+    for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention",
+                 "dl_mamba_conv", "dl_mamba_scan", "dl_sample_rows", "dl_argmax"):
+        getattr(L, name).restype = i32
+    _layers = L
+    return L
+
+
+def check_layers(rc: int, what: str = ""):
+    if rc != 0:
+        msg = layers_lib().dl_last_error().decode("utf-8", "replace")
         raise NativeLibraryError(f"{what} failed ({rc}): {msg}")
 
 

@@ -298,6 +298,93 @@ int dl_ipc_free(void* dev_ptr);
 int dl_peer_barrier(uint32_t* const* flags_on_peers /*host array*/, uint32_t* my_flags, int rank, int world,
                     uint32_t epoch, void* stream);
 
+/* ==== layer-list models: dense bf16 / f32 weights, latent attention, Mamba-2 ===================
+ * Built into libdllama_b200_layers.so (dense.cu, norms.cu, latent_attention.cu, mamba2.cu, plus the shared
+ * prep.cu and sampler.cu).  Activations between kernels are f32; `wtype` / `ctype`: 0 = f32, 1 = bf16. */
+enum { DL_DENSE_STORE = 0, DL_DENSE_RELU2 = 1, DL_DENSE_SIGMOID_MUL = 2, DL_DENSE_SOFTCAP = 3 };
+
+/* Y[b][m][n] = epi( sum_k X[b][m][k] * W[b][n][k] ),  b < batch (element strides *_bs).  round_x: the activation
+ * operand is rounded to bf16 on load (bf16 mode).  DL_DENSE_SIGMOID_MUL: aux[m][n] * sigmoid(.);
+ * DL_DENSE_SOFTCAP: param * tanh(. / param). */
+typedef struct {
+    const void* W; int wtype; long long ldw, w_bs;
+    const float* X; long long ldx, x_bs;
+    float* Y; long long ldy, y_bs;
+    int M, N, K, batch;
+    int round_x;
+    int epi;
+    const float* aux; long long ld_aux, aux_bs;
+    float param;
+} DlDenseArgs;
+int dl_dense(const DlDenseArgs* args /*host*/, void* stream);
+int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, void* stream);
+
+/* y[m] (+)= v / sqrt(mean(v^2) + eps) * scale per group of dim/groups values; v = x[rows ? rows[m] : m] (* silu(gate));
+ * scale = w, 1 + w (plus_one) or 1 (w NULL).  In place (y == x) is allowed without `accumulate`. */
+typedef struct {
+    const float* x; long long ldx;
+    const float* gate; long long ld_gate;
+    const float* w;
+    float* y; long long ldy;
+    const int* rows;
+    int M, dim, groups;
+    float eps;
+    int plus_one, accumulate;
+} DlNormArgs;
+int dl_rms_norm(const DlNormArgs* args /*host*/, void* stream);
+
+/* latent-attention cache writer: row m of kv[M][ld] = [rank | rot]; the first `rank` are RMS-normed (* norm_w), the
+ * first rope_dims of the last `rot` are rotated by the row's position (freqs: f64 [rope_dims / 2]); the token's
+ * cache line is cache[page][pos % page_size][rank + rot], page = block_table[slot][pos / page_size]. */
+typedef struct {
+    const float* kv; long long ld;
+    const float* norm_w; float eps;
+    int rank, rot, rope_dims;
+    const double* freqs;
+    const int* pos; const int* slot; const int* block_table;
+    int max_pages, page_size;
+    void* cache; int ctype;
+} DlLatentKvArgs;
+int dl_latent_kv_write(const DlLatentKvArgs* args /*host*/, int M, void* stream);
+int dl_rope_rows(float* x, long long ld, int M, int n_heads, int head_stride, int offset, int rope_dims,
+                 const double* freqs, const int* pos, void* stream);
+
+/* attention of M rows over the paged latent cache.  q_lat[M][n_heads][rank]: queries already multiplied by the
+ * key up-projection; q[M][ldq] holds each head's rotated part at q_head_stride * h + q_rot_offset.
+ * out[M][n_heads][rank] = softmax-weighted sum of the latents (the value up-projection follows as a dense product). */
+typedef struct {
+    const float* q_lat;
+    const float* q; long long ldq; int q_head_stride, q_rot_offset;
+    float* out;
+    int n_heads, rank, rot;
+    float scale;
+    const int* pos; const int* slot; const int* block_table;
+    int max_pages, page_size;
+    const void* cache; int ctype;
+} DlLatentAttnArgs;
+int dl_latent_attention(const DlLatentAttnArgs* args /*host*/, int M, void* stream);
+
+/* batch description for recurrent layers (device arrays): sequence n owns rows seq_rows[seq_start[n] .. seq_start[n+1])
+ * in position order, starting at position seq_pos0[n], with its state in slot seq_slot[n]; row_seq / pos are per row */
+typedef struct {
+    const int* pos; const int* row_seq;
+    const int* seq_start; const int* seq_rows; const int* seq_slot; const int* seq_pos0;
+} DlMambaBatch;
+/* out[M][channels] = silu(causal conv over in[row][in_off + ch] + bias); conv_state[slot][taps-1][channels] carries
+ * the last taps-1 inputs of each slot and is updated */
+int dl_mamba_conv(const DlMambaBatch* batch /*host*/, int M, int n_seq, const float* in, long long ld, int in_off,
+                  const void* w, const void* bias, int wtype, float* conv_state, float* out, int channels, int taps,
+                  void* stream);
+typedef struct {
+    const float* xbc; long long ld_xbc;      /* [M][x: heads*vdim | B: groups*state | C: groups*state] after conv + silu */
+    const float* dt; long long ld_dt;        /* raw dt of head h at dt[m * ld_dt + h] */
+    const float* dt_bias; const float* A_log; const float* D;   /* [heads] f32 */
+    float* y; long long ld_y;                /* [M][heads*vdim] */
+    float* ssm_state;                        /* [n_slots][heads][state][vdim] f32 */
+    int n_heads, vdim, state, groups;
+} DlMambaScanArgs;
+int dl_mamba_scan(const DlMambaBatch* batch /*host*/, int n_seq, const DlMambaScanArgs* args /*host*/, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
