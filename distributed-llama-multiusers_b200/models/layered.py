@@ -454,5 +454,80 @@ class LayerListEngine:
     def decode_greedy_host(self, tokens, positions, slots) -> List[int]:
         return self.decode_step_greedy(tokens, positions, slots, 0)
 
+    def sample_rows(self, logits, temperature, topp, coin, tokens_out):
+        """Device sampler of the batching loop (temperature / top-p / coin per row), from this engine's library."""
+        self.L.sample_rows(logits, temperature, topp, coin, tokens_out)
+
     def close(self):
         torch.cuda.synchronize()
+
+
+# --------------------------------------------------------------------------------------------------
+# random models (tests, benchmarks, the smoke run): same files a trained model would come in
+# --------------------------------------------------------------------------------------------------
+def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random bf16 weights for every tensor the configuration calls for (matrices ~ N(0, 1/in), norm weights small
+    around zero, decays and step-size biases in the range where the recurrence neither dies nor saturates)."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = int(config["width"]), int(config["vocab"])
+
+    def mat(o, i, gain=1.0):
+        return (torch.randn(o, i, generator=g) * gain / math.sqrt(i)).to(torch.bfloat16)
+
+    def small(n, s=0.1):
+        return (torch.randn(n, generator=g) * s).to(torch.bfloat16)
+
+    t = {"embed": (torch.randn(V, W, generator=g)).to(torch.bfloat16), "final.norm": small(W), "head": mat(V, W)}
+    for i, l in enumerate(config["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        t[p + "norm1"], t[p + "norm1b"] = small(W), small(W)
+        if l["type"] == "latent_attention":
+            H, dn, dr, dv, qr, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            t[p + "mix.dq"], t[p + "mix.dq.norm"] = mat(qr, W), 1 + small(qr)
+            t[p + "mix.uq"] = mat(H * (dn + dr), qr, 2.0)
+            if "kv_from" not in m:
+                t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = mat(r + dr, W), 1 + small(r)
+            t[p + "mix.uk"], t[p + "mix.uv"] = mat(H * dn, r, 2.0), mat(H * dv, r)
+            t[p + "mix.g"], t[p + "mix.o"] = mat(H * dv, W), mat(W, H * dv)
+        elif l["type"] == "mamba2":
+            H, P, N, G, taps = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            inner, ch = H * P, H * P + 2 * G * N
+            t[p + "mix.in"] = mat(2 * inner + 2 * G * N + H, W)
+            t[p + "mix.conv"], t[p + "mix.conv.b"] = mat(ch, taps, 1.5), small(ch)
+            t[p + "mix.dt_bias"] = (torch.rand(H, generator=g) * 2 - 2).to(torch.bfloat16)
+            t[p + "mix.A_log"] = torch.log(torch.rand(H, generator=g) * 1.5 + 0.25).to(torch.bfloat16)
+            t[p + "mix.D"], t[p + "mix.norm"] = 1 + small(H), 1 + small(inner)
+            t[p + "mix.o"] = mat(W, inner)
+        else:
+            raise ValueError(f"layer {i}: unknown mixer type {l['type']!r}")
+        if l.get("mlp"):
+            t[p + "norm2"], t[p + "norm2b"] = small(W), small(W)
+            t[p + "mlp.up"], t[p + "mlp.down"] = mat(l["mlp"]["ff"], W), mat(W, l["mlp"]["ff"])
+    return t
+
+
+def write_random_model(model_dir: str, config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """config.json + model.safetensors of a random model; returns the tensors written."""
+    from ..formats.safetensors import write_safetensors
+    os.makedirs(model_dir, exist_ok=True)
+    with open(os.path.join(model_dir, "config.json"), "w") as f:
+        json.dump(config, f, indent=1)
+    tensors = random_tensors(config, seed)
+    write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors)
+    return tensors
+
+
+def example_config(width: int = 192, vocab: int = 320, blocks: int = 2, heads: int = 4) -> dict:
+    """A small Ribivik-shaped configuration: `blocks` x (mamba2 layer without feed-forward, latent-attention layer
+    with one); from the third attention layer on, layers read the cache of the second."""
+    layers = []
+    for b in range(blocks):
+        layers.append({"type": "mamba2", "mlp": None,
+                       "mixer": {"heads": heads, "vdim": 24, "state": 16, "groups": 2, "conv": 3, "norm_groups": 2}})
+        mixer = {"heads": heads, "dim": 40, "rot_dim": 8, "vdim": 24, "q_rank": 48, "kv_rank": 56,
+                 "scale": 1.0 / math.sqrt(48), "rot": {"base": 10000.0, "dims": 8}}
+        if b >= 2:
+            mixer["kv_from"] = 3
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": 2 * width}})
+    return {"architecture": "Ribivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 25.0,
+            "layers": layers}

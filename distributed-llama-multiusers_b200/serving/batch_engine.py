@@ -87,8 +87,11 @@ class BatchEngine:
         dev = getattr(engine, "device", torch.device("cpu"))
         self._device_sampler = dev.type == "cuda" and os.environ.get("DLLAMA_HOST_SAMPLER", "0") != "1"
         if self._device_sampler:
-            from ..ops import kernels as _K
-            self._K = _K
+            # an engine with a kernel library of its own brings its binding of the sampler
+            self._sample_rows = getattr(engine, "sample_rows", None)
+            if self._sample_rows is None:
+                from ..ops import kernels as _K
+                self._sample_rows = _K.sample_rows
             R = self.max_rows
             self._h_params = torch.zeros(3, R, dtype=torch.float32).pin_memory()      # temperature | topp | coin
             self._d_params = torch.zeros(3, R, dtype=torch.float32, device=dev)
@@ -197,7 +200,7 @@ class BatchEngine:
                     hp[0, i], hp[1, i] = r.temperature, r.top_p
                     hp[2, i] = r._sampler.coin() if r.temperature != 0.0 else 0.0
             self._d_params.copy_(self._h_params, non_blocking=True)
-            self._K.sample_rows(logits[:n_s], self._d_params[0], self._d_params[1], self._d_params[2], self._d_tok)
+            self._sample_rows(logits[:n_s], self._d_params[0], self._d_params[1], self._d_params[2], self._d_tok)
             self._h_tok.copy_(self._d_tok, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             sampled = self._h_tok[:n_s].tolist()

@@ -1,0 +1,58 @@
+"""Model directories without a GPU: the safetensors container, the configuration reader, the architecture registry,
+the random-model writer, and the oracle's own consistency."""
+import json
+import os
+
+import pytest
+import torch
+
+import layered_oracle as O
+from dllama_b200.formats.safetensors import SafetensorsFile, write_safetensors
+from dllama_b200.models import registry
+from dllama_b200.models.layered import LayerListConfig, example_config, random_tensors, write_random_model
+
+
+def test_safetensors_round_trip(tmp_path):
+    t = {"a.b": torch.randn(3, 5).to(torch.bfloat16), "c": torch.arange(7, dtype=torch.int32), "d": torch.randn(2, 2, 2),
+         "e": torch.randn(4).to(torch.float16)}
+    p = str(tmp_path / "x.safetensors")
+    write_safetensors(p, t)
+    with open(p, "rb") as f:
+        n = int.from_bytes(f.read(8), "little")
+        head = json.loads(f.read(n))
+    assert head["a.b"] == {"dtype": "BF16", "shape": [3, 5], "data_offsets": head["a.b"]["data_offsets"]}
+    st = SafetensorsFile(p)
+    assert set(st.names()) == set(t) and st.shape("d") == (2, 2, 2) and "zz" not in st
+    for k, v in t.items():
+        assert st.tensor(k).dtype == v.dtype and torch.equal(st.tensor(k), v)
+    st.close()
+    with open(p, "r+b") as f:                       # a tensor whose byte range does not match its shape is refused
+        f.seek(8)
+        f.write(json.dumps(head).replace('"shape":[3,5]', '"shape":[3,6]').encode()[:n])
+    with pytest.raises(ValueError):
+        SafetensorsFile(p).tensor("a.b")
+
+
+def test_configuration_and_registry(tmp_path):
+    cfg = example_config(blocks=3)
+    d = str(tmp_path / "m")
+    tensors = write_random_model(d, cfg, seed=1)
+    assert registry.is_model_dir(d) and not registry.is_model_dir(str(tmp_path / "nope"))
+    assert registry.architecture_of(d) == "Ribivik" and "Ribivik" in registry.ARCHITECTURES
+    c = LayerListConfig.load(d)
+    assert c.vocab_size == cfg["vocab"] and c.n_layers == 6 and c.layers[0].mlp is None and c.layers[5].mixer["kv_from"] == 3
+    assert "l5.mix.dkv" not in tensors and "l3.mix.dkv" in tensors and "l0.mlp.up" not in tensors
+    assert tensors["l0.mix.in"].shape == (2 * 96 + 2 * 2 * 16 + 4, 192) and tensors["l1.mix.uq"].shape == (4 * 48, 48)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump({**cfg, "architecture": "NoSuchDesign"}, f)
+    with pytest.raises(ValueError):
+        registry.engine_for_dir(d)
+
+
+def test_oracle_prefix_property():
+    """Causality of the oracle itself: the logits of a prefix do not change when tokens are appended."""
+    cfg = example_config(width=48, vocab=40, blocks=3, heads=2)
+    t = random_tensors(cfg, seed=2)
+    toks = torch.randint(0, 40, (20,), generator=torch.Generator().manual_seed(3)).tolist()
+    a, b = O.model_logits(t, cfg, toks), O.model_logits(t, cfg, toks[:11])
+    assert torch.allclose(a[:11], b, atol=1e-9)
