@@ -61,10 +61,10 @@ def _run(cmd, verbose, log_path=None):
         sys.stdout.write(p.stdout)
 
 
-# sources of the layer-list model library; prep.cu (error plumbing, argmax) and sampler.cu are shared with the other
-# one (their objects are compiled once), the rest belongs to this library alone
+# sources of the layer-list model library; prep.cu (error plumbing, argmax), sampler.cu and gemm_wh_tc.cu (the tcgen05
+# GEMM on pre-tiled operands) are shared with the other one (their objects are compiled once), the rest is its own
 LAYERS_OWN = ["dense.cu", "latent_attention.cu", "mamba2.cu", "norms.cu"]
-LAYERS_SHARED = ["prep.cu", "sampler.cu"]
+LAYERS_SHARED = ["gemm_wh_tc.cu", "prep.cu", "sampler.cu"]
 
 
 def build_cuda(force=False, verbose=False) -> str:

@@ -233,3 +233,52 @@ extern "C" int dl_dense(const DlDenseArgs* args, void* stream) {
     LAYER_CHECK_LAUNCH("dl_dense");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// operand images of the tcgen05 GEMM (gemm_wh_tc.cu) for bf16 weights: element (row, k) of a 128 x 128 tile lives at
+//   (row >> 3) * 2048 + (k >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2      (8 x 16 B core matrices, K-major)
+// weights: tiles [row_tile][k_tile][32 KB]; activations: [k_tile][ncap / 8][2048 B].  One thread per 8 K values.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) wh_from_dense_kernel(const __nv_bfloat16* __restrict__ w, int N, int K, long long ldw,
+                                                            uint8_t* __restrict__ wh, int KT) {
+    const int tile = blockIdx.x, rt = tile / KT, kt = tile % KT;
+    uint8_t* out = wh + (size_t)tile * 32768;
+    for (int i = threadIdx.x; i < 128 * 16; i += blockDim.x) {
+        const int r = i >> 4, c = i & 15;
+        const int row = rt * 128 + r, k0 = kt * 128 + c * 8;
+        __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (row < N && k0 + j < K) ? w[(size_t)row * ldw + k0 + j] : __float2bfloat16_rn(0.f);
+        *reinterpret_cast<uint4*>(out + (size_t)(r >> 3) * 2048 + c * 128 + (r & 7) * 16) = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
+__global__ void __launch_bounds__(256) xh_from_rows_kernel(const float* __restrict__ x, long long ldx, int M, int K, int ncap,
+                                                           uint8_t* __restrict__ xh) {
+    const int g = blockIdx.x, kt = blockIdx.y;           // row group of 8, k tile
+    uint8_t* out = xh + ((size_t)kt * (ncap >> 3) + g) * 2048;
+    for (int i = threadIdx.x; i < 8 * 16; i += blockDim.x) {
+        const int r = i & 7, c = i >> 3;
+        const int m = g * 8 + r, k0 = kt * 128 + c * 8;
+        __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn((m < M && k0 + j < K) ? x[(size_t)m * ldx + k0 + j] : 0.f);
+        *reinterpret_cast<uint4*>(out + c * 128 + r * 16) = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
+extern "C" int dl_wh_from_dense(const void* w, int N, int K, long long ldw, uint8_t* wh, void* stream) {
+    if (N < 1 || K < 1) { dl_set_error("dl_wh_from_dense: empty matrix"); return -1; }
+    const int KT = (K + 127) / 128, RT = (N + 127) / 128;
+    wh_from_dense_kernel<<<RT * KT, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)w, N, K, ldw, wh, KT);
+    LAYER_CHECK_LAUNCH("dl_wh_from_dense");
+    return 0;
+}
+
+extern "C" int dl_xh_from_rows(const float* x, long long ldx, int M, int K, int ncap, uint8_t* xh, void* stream) {
+    if (M < 1 || K < 1 || ncap % 8 != 0 || ncap < M) { dl_set_error("dl_xh_from_rows: bad M=%d / ncap=%d", M, ncap); return -1; }
+    dim3 grid((M + 7) / 8, (K + 127) / 128);
+    xh_from_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, M, K, ncap, xh);
+    LAYER_CHECK_LAUNCH("dl_xh_from_rows");
+    return 0;
+}

@@ -173,6 +173,26 @@ DL_DEVINL void epilogue_rows(const DlEpilogue& e, const float* out_s, int out_ld
                 }
             }
         }
+    } else if (e.kind == DL_EPI_DENSE) {
+        // dense-weight models: an element-wise op on the f32 result, then a plain store (one destination)
+        if (tid < rows) {
+            const int grow = grow0 + tid;
+            if (grow < d_real) {
+                const size_t ld = (size_t)e.ld, ald = (size_t)e.dense_aux_ld;
+                float* d0 = e.dst[0] + (size_t)e.dst_off + (size_t)m0 * ld + grow;
+                const float* aux = e.dense_aux != nullptr ? e.dense_aux + (size_t)m0 * ald + grow : nullptr;
+                const int op = e.dense_op;
+                const float prm = e.dense_param;
+#pragma unroll 4
+                for (int m = m_first; m < M; m += m_step) {
+                    float v = out_s[m * out_ld + tid];
+                    if (op == DL_DENSE_RELU2) { v = fmaxf(v, 0.0f); v *= v; }
+                    else if (op == DL_DENSE_SIGMOID_MUL) v = aux[m * ald] / (1.0f + expf(-v));
+                    else if (op == DL_DENSE_SOFTCAP) v = prm * tanhf(v / prm);
+                    d0[m * ld] = v;
+                }
+            }
+        }
     } else {   // DL_EPI_SILU_MUL: rows interleaved (gate_i, up_i); rows/2 hidden values per tile.
         // thread j < rows/2 owns hidden value j: reads local rows 2j, 2j+1; a warp = one Q80 block.
         const int nh = rows >> 1;

@@ -37,6 +37,7 @@ struct WhArgs {
     int piece;                         // bytes per bulk copy (4096 / 8192 / 16384)
     int pf_dist, pf_mask;              // weight tiles are pulled into L2 pf_dist k-steps ahead by the CTAs whose activation tile index & pf_mask == 0
     int dbg;                           // timing experiments (results invalid): 1 = no epilogue work, 2 = no MMAs, 4 = no activation copies
+    int bf16;                          // both operand images hold bf16 instead of fp16 (dense-weight models)
     unsigned long long* tr;
     DlEpilogue epi;
 };
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
     } else if (warp == 1) {
         if (CG == 1 || crank == 0) {
             // ------------------------------------ MMA issuer ------------------------------------
-            const uint32_t idesc = umma_idesc_f16_f32(128 * CG, WT_NT);
+            const uint32_t idesc = umma_idesc_f16_f32(128 * CG, WT_NT) | (a.bf16 ? ((1u << 7) | (1u << 10)) : 0u);   // a_format = b_format = BF16
             const uint32_t desc_hi = (2048u >> 4) | (1u << 14);      // SBO 2048 B (8-row groups), descriptor version 1
             uint32_t it = 0, tcount = 0;
             for (int t = cid; t < a.n_tiles; t += ncl, tcount++) {
@@ -343,7 +344,8 @@ extern "C" int dl_q40t_to_wh(const uint8_t* q40t, int d, int n, uint8_t* wh, voi
     return 0;
 }
 
-// force_cg: 0 = pairs when the row-tile count is even, 1 = single CTAs (for tests and comparisons)
+// force_cg: bit 0: 0 = pairs when the row-tile count is even, 1 = single CTAs (for tests and comparisons);
+// bit 1: the images hold bf16 (written by dl_wh_from_dense / dl_xh_from_rows) instead of fp16
 extern "C" int dl_gemm_wh_tc(const uint8_t* wh, int d, int n, const uint8_t* xh, int ncap, int M, const DlEpilogue* epi,
                              int force_cg, int pdl, void* stream) {
     if (n % 128 != 0) { dl_set_error("dl_gemm_wh_tc: n=%d not a multiple of 128", n); return -1; }
@@ -354,7 +356,8 @@ extern "C" int dl_gemm_wh_tc(const uint8_t* wh, int d, int n, const uint8_t* xh,
     a.row_tiles = (d + 127) / 128;
     a.KT = n / 128; a.ncap = ncap; a.M = M;
     a.m_tiles = (M + WT_NT - 1) / WT_NT;
-    const int cg = (force_cg == 1 || (a.row_tiles & 1)) ? 1 : 2;
+    const int cg = ((force_cg & 1) || (a.row_tiles & 1)) ? 1 : 2;
+    a.bf16 = (force_cg & 2) ? 1 : 0;
     a.n_tiles = (a.row_tiles / cg) * a.m_tiles;
     const int n_sms = dl_device_sm_count();
     int grid = (n_sms / cg) * cg;

@@ -88,6 +88,25 @@ def rotary_frequencies(base: float, dims: int) -> torch.Tensor:
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
 
 
+class DenseWeight:
+    """A matrix [N][K] (or per-head matrices [H][N][K]) in the engine's weight type, plus -- in bf16 mode -- its image
+    for the tensor-core GEMM (one per head), which serves batches of TC_MIN_ROWS rows and more."""
+
+    def __init__(self, t: torch.Tensor, tc: bool):
+        from ..ops import layers as L
+        self.t = t
+        self.N, self.K = int(t.shape[-2]), int(t.shape[-1])
+        self.wh = None
+        if tc and t.dtype == torch.bfloat16:
+            self.wh = [L.make_wh(t[h]) for h in range(t.shape[0])] if t.dim() == 3 else L.make_wh(t)
+
+    def nbytes(self) -> int:
+        return self.t.numel() * self.t.element_size()
+
+
+TC_MIN_ROWS = int(os.environ.get("DLLAMA_LAYERS_TC_MIN_ROWS", "32"))
+
+
 # --------------------------------------------------------------------------------------------------
 # mixers
 # --------------------------------------------------------------------------------------------------
@@ -106,15 +125,15 @@ class LatentAttentionMixer:
             raise ValueError(f"layer {index}: rotary dims {self.rope_dims} do not fit rot_dim {self.dr}")
         self.freqs = rotary_frequencies(float(m["rot"]["base"]), self.rope_dims).to(eng.device)
         self.kv_from = m.get("kv_from")
-        W, V = eng.weight, eng.vector
-        self.w_dq, self.dq_norm, self.w_uq = W(prefix + "dq"), V(prefix + "dq.norm"), W(prefix + "uq")
-        self.w_g, self.w_o = W(prefix + "g"), W(prefix + "o")
+        W, V, D = eng.weight, eng.vector, eng.dense_weight
+        self.w_dq, self.dq_norm, self.w_uq = D(W(prefix + "dq")), V(prefix + "dq.norm"), D(W(prefix + "uq"))
+        self.w_g, self.w_o = D(W(prefix + "g")), D(W(prefix + "o"))
         H, dn, dv, r = self.H, self.dn, self.dv, self.rank
         # key up-projection per head, transposed, so that  q_lat[h] = U_k,h^T q_h  is a product against rows of K = dn
-        self.w_uk_t = W(prefix + "uk").reshape(H, dn, r).transpose(1, 2).contiguous()
-        self.w_uv = W(prefix + "uv").reshape(H, dv, r).contiguous()
+        self.w_uk_t = D(W(prefix + "uk").reshape(H, dn, r).transpose(1, 2).contiguous())
+        self.w_uv = D(W(prefix + "uv").reshape(H, dv, r).contiguous())
         if self.kv_from is None:
-            self.w_dkv, self.dkv_norm = W(prefix + "dkv"), V(prefix + "dkv.norm")
+            self.w_dkv, self.dkv_norm = D(W(prefix + "dkv")), V(prefix + "dkv.norm")
             self.cache = torch.zeros(eng.n_pages, PAGE, r + self.dr, dtype=eng.wdtype, device=eng.device)
         else:
             self.cache = None                      # bound to the owner's cache once all layers exist
@@ -135,28 +154,28 @@ class LatentAttentionMixer:
 
     def weight_bytes(self) -> int:
         ts = [self.w_dq, self.w_uq, self.w_g, self.w_o, self.w_uk_t, self.w_uv] + ([self.w_dkv] if self.kv_from is None else [])
-        return sum(t.numel() * t.element_size() for t in ts)
+        return sum(t.nbytes() for t in ts)
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
-        e, L, rx = self.eng, self.eng.L, self.eng.round_x
+        e, L = self.eng, self.eng.L
         H, dn, dr, dv, r = self.H, self.dn, self.dr, self.dv, self.rank
         cq, q, o, og = (e.buf(n) for n in ("cq", "q", "o", "og"))
         q_lat, o_lat = e.buf("q_lat", H * r), e.buf("o_lat", H * r)          # read as [M][H][rank], no row padding
         hd = dn + dr
-        L.dense(self.w_dq, h, cq, M, rx)
+        e.mm(self.w_dq, h, cq, M, src="h")
         L.rms_norm(cq, cq, M, self.q_rank, e.cfg.norm_eps, w=self.dq_norm)
-        L.dense(self.w_uq, cq, q, M, rx)
+        e.mm(self.w_uq, cq, q, M)
         L.rope_rows(q, M, H, hd, dn, self.rope_dims, self.freqs, e.pos)
         if self.kv_from is None:
             kv = e.buf("kv")
-            L.dense(self.w_dkv, h, kv, M, rx)
+            e.mm(self.w_dkv, h, kv, M, src="h")
             L.latent_kv_write(kv, M, self.dkv_norm, e.cfg.norm_eps, r, dr, self.rope_dims, self.freqs, e.pos, e.slot,
                               e.block_table, self.cache)
-        L.dense_heads(self.w_uk_t, q, q_lat, M, rx, hd, r)
+        e.mm_heads(self.w_uk_t, q, q_lat, M, hd, r)
         L.latent_attention(q_lat, q, hd, dn, o_lat, M, H, r, dr, self.scale, e.pos, e.slot, e.block_table, self.cache)
-        L.dense_heads(self.w_uv, o_lat, o, M, rx, r, dv)
-        L.dense(self.w_g, h, og, M, rx, epi=L.DENSE_SIGMOID_MUL, aux=o)
-        L.dense(self.w_o, og, y, M, rx)
+        e.mm_heads(self.w_uv, o_lat, o, M, r, dv)
+        e.mm(self.w_g, h, og, M, epi=L.DENSE_SIGMOID_MUL, aux=o, src="h")
+        e.mm(self.w_o, og, y, M)
 
 
 class Mamba2Mixer:
@@ -171,12 +190,12 @@ class Mamba2Mixer:
         self.channels = self.inner + 2 * self.G * self.N
         if self.H % self.G or self.inner % self.norm_groups:
             raise ValueError(f"layer {index}: heads / groups / norm_groups do not divide")
-        W, V = eng.weight, eng.vector
-        self.w_in, self.w_o = W(prefix + "in"), W(prefix + "o")
+        W, V, D = eng.weight, eng.vector, eng.dense_weight
+        self.w_in, self.w_o = D(W(prefix + "in")), D(W(prefix + "o"))
         self.w_conv, self.b_conv = W(prefix + "conv"), W(prefix + "conv.b")
         self.dt_bias, self.A_log, self.D, self.norm = (V(prefix + n) for n in ("dt_bias", "A_log", "D", "norm"))
-        if tuple(self.w_in.shape) != (2 * self.inner + 2 * self.G * self.N + self.H, eng.cfg.width):
-            raise ValueError(f"layer {index}: input projection has shape {tuple(self.w_in.shape)}")
+        if tuple(self.w_in.t.shape) != (2 * self.inner + 2 * self.G * self.N + self.H, eng.cfg.width):
+            raise ValueError(f"layer {index}: input projection has shape {tuple(self.w_in.t.shape)}")
         # the slot's recurrent state: S [heads][state][vdim] and the last taps-1 convolution inputs, both f32
         self.ssm_state = torch.zeros(eng.n_slots, self.H, self.N, self.P, dtype=torch.float32, device=eng.device)
         self.conv_state = torch.zeros(eng.n_slots, max(1, self.taps - 1), self.channels, dtype=torch.float32, device=eng.device)
@@ -188,19 +207,19 @@ class Mamba2Mixer:
         pass
 
     def weight_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o, self.w_conv))
+        return self.w_in.nbytes() + self.w_o.nbytes() + self.w_conv.numel() * self.w_conv.element_size()
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
-        e, L, rx = self.eng, self.eng.L, self.eng.round_x
+        e, L = self.eng, self.eng.L
         zx, ys, yn = e.buf("zx"), e.buf("ys"), e.buf("yn")
         xbc = e.buf("xbc", self.channels)
-        L.dense(self.w_in, h, zx, M, rx)
+        e.mm(self.w_in, h, zx, M, src="h")
         L.mamba_conv(e.mamba_batch, M, e.n_seq, zx, self.inner, self.w_conv, self.b_conv, self.conv_state, xbc)
         dt = zx[:, 2 * self.inner + 2 * self.G * self.N:]
         L.mamba_scan(e.mamba_batch, e.n_seq, xbc, dt, self.dt_bias, self.A_log, self.D, ys, self.ssm_state, self.H, self.P,
                      self.N, self.G)
         L.rms_norm(ys, yn, M, self.inner, e.cfg.norm_eps, w=self.norm, groups=self.norm_groups, gate=zx)
-        L.dense(self.w_o, yn, y, M, rx)
+        e.mm(self.w_o, yn, y, M)
 
 
 class DenseFeedForward:
@@ -209,19 +228,19 @@ class DenseFeedForward:
     def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
         self.eng = eng
         self.ff = int(m["ff"])
-        self.w_up, self.w_down = eng.weight(prefix + "up"), eng.weight(prefix + "down")
+        self.w_up, self.w_down = eng.dense_weight(eng.weight(prefix + "up")), eng.dense_weight(eng.weight(prefix + "down"))
 
     def scratch(self) -> Dict[str, int]:
         return {"up": self.ff}
 
     def weight_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+        return self.w_up.nbytes() + self.w_down.nbytes()
 
     def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
         e, L = self.eng, self.eng.L
         up = e.buf("up")
-        L.dense(self.w_up, h, up, M, e.round_x, epi=L.DENSE_RELU2)
-        L.dense(self.w_down, up, y, M, e.round_x)
+        e.mm(self.w_up, h, up, M, epi=L.DENSE_RELU2, src="h")
+        e.mm(self.w_down, up, y, M)
 
 
 MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer}
@@ -250,7 +269,7 @@ class _Layer:
 class LayerListEngine:
     def __init__(self, model_path: str, rank: int = 0, world: int = 1, group=None, max_rows: int = 32, n_slots: int = 4,
                  max_seq_len: int = 2048, dtype: str = "bfloat16", n_pages: Optional[int] = None,
-                 device: Optional[torch.device] = None, **_unused):
+                 device: Optional[torch.device] = None, tensor_cores: Optional[bool] = None, **_unused):
         if world != 1:
             raise NotImplementedError("layer-list models run on one GPU (no tensor-parallel slicing of their mixers yet)")
         if dtype not in ("bfloat16", "float32"):
@@ -264,6 +283,12 @@ class LayerListEngine:
         self.dtype = dtype
         self.wdtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
         self.round_x = dtype == "bfloat16"
+        # bf16 mode: batches of TC_MIN_ROWS rows and more run their matrix products on the tcgen05 GEMM (operand images
+        # made once per weight at load time, once per activation matrix at run time); fewer rows stream the weights
+        if tensor_cores is None:
+            tensor_cores = os.environ.get("DLLAMA_LAYERS_TC", "1") != "0"
+        self.tc = bool(tensor_cores) and self.round_x and int(max_rows) >= TC_MIN_ROWS
+        self._kmax = 0
         self.max_rows, self.n_slots = int(max_rows), int(n_slots)
         self.seq_len = self.cfg.seq_len = int(max_seq_len)
         self.max_pages = (self.seq_len + PAGE - 1) // PAGE
@@ -277,7 +302,7 @@ class LayerListEngine:
             if tuple(self.embed.shape) != (self.cfg.vocab, self.cfg.width):
                 raise ValueError(f"embed has shape {tuple(self.embed.shape)}")
             self.layers = [_Layer(self, i, spec) for i, spec in enumerate(self.cfg.layers)]
-            self.final_norm, self.head = self.vector("final.norm"), self.weight("head")
+            self.final_norm, self.head = self.vector("final.norm"), self.dense_weight(self.weight("head"))
         finally:
             self._st.close()
         mixers = [l.mixer for l in self.layers]
@@ -292,6 +317,11 @@ class LayerListEngine:
                         widths[name] = max(widths.get(name, 0), w)
         self._bufs = {n: torch.zeros(R * w, dtype=torch.float32, device=dev) for n, w in widths.items()}
         self._widths = widths
+        self.ncap = (R + 7) // 8 * 8
+        self._xh = {}
+        if self.tc:       # activation slabs: one kept for a sublayer's input (several products read it), one for the rest
+            n = L.xh_bytes(self._kmax, self.ncap)
+            self._xh = {k: torch.zeros(n, dtype=torch.uint8, device=dev) for k in ("h", "tmp")}
         self.x = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
         self.hn = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
         self.y = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
@@ -313,6 +343,7 @@ class LayerListEngine:
         self.block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32, device=dev)
         self.h_block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32).pin_memory()
         self._staging_ev: Optional[torch.cuda.Event] = None
+        self._xh_h_ready = False
         self.layer_probe = None              # a list: forward() appends a copy of the residual stream after every layer
         torch.cuda.synchronize()
 
@@ -329,6 +360,37 @@ class LayerListEngine:
             raise KeyError(f"model.safetensors has no tensor {name!r}")
         return self._st.tensor(name).to(torch.float32).to(self.device).contiguous()
 
+    def dense_weight(self, t: torch.Tensor) -> DenseWeight:
+        self._kmax = max(self._kmax, int(t.shape[-1]))
+        return DenseWeight(t, self.tc)
+
+    def mm(self, w: DenseWeight, x: torch.Tensor, y: torch.Tensor, M: int, epi: int = 0, aux=None, param: float = 0.0,
+           src: str = "tmp"):
+        """y[:M] = epi(x[:M] @ w^T).  src="h": x is the current sublayer input; its tensor-core image is made by the
+        first product that reads it (begin_sublayer() marks it stale) and shared by the others."""
+        L = self.L
+        if w.wh is None or M < TC_MIN_ROWS:
+            L.dense(w.t, x, y, M, self.round_x, epi=epi, aux=aux, param=param)
+            return
+        xh = self._xh[src]
+        if src != "h" or not self._xh_h_ready:
+            L.xh_from_rows(x, M, w.K, self.ncap, xh)
+            self._xh_h_ready = src == "h" or self._xh_h_ready
+        L.dense_tc(w.wh, w.N, w.K, xh, self.ncap, y, M, epi=epi, aux=aux, param=param)
+
+    def mm_heads(self, w: DenseWeight, x: torch.Tensor, y: torch.Tensor, M: int, x_head_stride: int, y_head_stride: int):
+        """Per head h: y[:M, h*ys : h*ys+N] = x[:M, h*xs : h*xs+K] @ w[h]^T."""
+        L = self.L
+        if w.wh is None or M < TC_MIN_ROWS:
+            L.dense_heads(w.t, x, y, M, self.round_x, x_head_stride, y_head_stride)
+            return
+        for h in range(w.t.shape[0]):
+            L.xh_from_rows(x[:, h * x_head_stride:], M, w.K, self.ncap, self._xh["tmp"])
+            L.dense_tc(w.wh[h], w.N, w.K, self._xh["tmp"], self.ncap, y[:, h * y_head_stride:], M)
+
+    def begin_sublayer(self):
+        self._xh_h_ready = False
+
     def buf(self, name: str, width: Optional[int] = None) -> torch.Tensor:
         """Scratch `name` as [max_rows][width] (default: the width it was sized for)."""
         w = width or self._widths[name]
@@ -336,7 +398,7 @@ class LayerListEngine:
 
     def weight_bytes(self) -> int:
         n = sum(l.mixer.weight_bytes() + (l.ff.weight_bytes() if l.ff else 0) for l in self.layers)
-        return n + self.head.numel() * self.head.element_size()
+        return n + self.head.nbytes()
 
     # ---- slots / pages ---------------------------------------------------------------------------
     def usable_pages(self) -> int:
@@ -406,20 +468,23 @@ class LayerListEngine:
         L.embed_rows(self.embed, self.tokens, x, M)
         for l in self.layers:
             L.rms_norm(x, hn, M, W, eps, w=l.norm1, plus_one=True)
+            self.begin_sublayer()
             l.mixer.forward(hn, y, M)
             L.rms_norm(y, x, M, W, eps, w=l.norm1b, plus_one=True, accumulate=True)
             if l.ff is not None:
                 L.rms_norm(x, hn, M, W, eps, w=l.norm2, plus_one=True)
+                self.begin_sublayer()
                 l.ff.forward(hn, y, M)
                 L.rms_norm(y, x, M, W, eps, w=l.norm2b, plus_one=True, accumulate=True)
             if self.layer_probe is not None:
                 self.layer_probe.append(x[:M].clone())
         if n_logits:
             L.rms_norm(x, hn, n_logits, W, eps, w=self.final_norm, plus_one=True, rows=self.logit_rows)
+            self.begin_sublayer()
             if cfg.logit_softcap > 0:
-                L.dense(self.head, hn, self.logits, n_logits, self.round_x, epi=L.DENSE_SOFTCAP, param=cfg.logit_softcap)
+                self.mm(self.head, hn, self.logits, n_logits, epi=L.DENSE_SOFTCAP, param=cfg.logit_softcap)
             else:
-                L.dense(self.head, hn, self.logits, n_logits, self.round_x)
+                self.mm(self.head, hn, self.logits, n_logits)
 
     @torch.no_grad()
     def forward(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int], logits_from: int = 0,

@@ -10,8 +10,8 @@ from typing import Optional
 import torch
 
 from . import lib
-from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
-                  DlLatentAttnArgs, DlLatentKvArgs, DlMambaBatch, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
+from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
+                  DlEpilogue, DlLatentAttnArgs, DlLatentKvArgs, DlMambaBatch, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
 
@@ -70,6 +70,45 @@ def dense_heads(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor, M: int, round
     a.round_x, a.epi = 1 if round_x else 0, DENSE_STORE
     a.aux, a.ld_aux, a.aux_bs, a.param = None, 0, 0, 0.0
     check_layers(layers_lib().dl_dense(a, _stream()), "dl_dense")
+    lib.count_launch()
+
+
+# ---- tensor-core path (bf16 weights, many rows): the tcgen05 GEMM of gemm_wh_tc.cu on pre-tiled operand images -----
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def make_wh(w: torch.Tensor) -> torch.Tensor:
+    """bf16 [N][K] (rows may be strided) -> the weight image of the tcgen05 GEMM (allocates; zero-padded to 128 x 128 tiles)."""
+    assert w.dtype == torch.bfloat16 and w.stride(1) == 1
+    N, K = w.shape
+    out = torch.empty(int(layers_lib().dl_wh_bytes(N, _round_up(K, 128))), dtype=torch.uint8, device=w.device)
+    check_layers(layers_lib().dl_wh_from_dense(w.data_ptr(), N, K, w.stride(0), out.data_ptr(), _stream()), "dl_wh_from_dense")
+    lib.count_launch()
+    return out
+
+
+def xh_bytes(K: int, ncap: int) -> int:
+    return _round_up(K, 128) // 128 * (ncap // 8) * 2048
+
+
+def xh_from_rows(x: torch.Tensor, M: int, K: int, ncap: int, xh: torch.Tensor):
+    """Columns [0, K) of the first M rows of f32 x -> bf16 activation slabs of the tcgen05 GEMM."""
+    assert xh.numel() >= xh_bytes(K, ncap)
+    check_layers(layers_lib().dl_xh_from_rows(x.data_ptr(), x.stride(0), M, K, ncap, xh.data_ptr(), _stream()), "dl_xh_from_rows")
+    lib.count_launch()
+
+
+def dense_tc(wh: torch.Tensor, N: int, K: int, xh: torch.Tensor, ncap: int, y: torch.Tensor, M: int, epi: int = DENSE_STORE,
+             aux: Optional[torch.Tensor] = None, param: float = 0.0):
+    """y[:M, :N] = epi(x @ w^T) from the two operand images (bf16 x bf16 -> f32 in tensor memory)."""
+    e = DlEpilogue()
+    e.kind, e.n_dst, e.ld, e.dst_off = EPI_DENSE, 1, y.stride(0), 0
+    e.dst[0] = y.data_ptr()
+    e.dense_op, e.dense_param = epi, param
+    e.dense_aux, e.dense_aux_ld = _p(aux), (aux.stride(0) if aux is not None else 0)
+    check_layers(layers_lib().dl_gemm_wh_tc(wh.data_ptr(), N, _round_up(K, 128), xh.data_ptr(), ncap, M, e, 2, 0, _stream()),
+                 "dl_gemm_wh_tc")
     lib.count_launch()
 
 

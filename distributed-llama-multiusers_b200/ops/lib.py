@@ -14,7 +14,7 @@ HOST_LIB_PATH = os.path.join(_PKG, "lib", "libdllama_b200_host.so")
 LAYERS_LIB_PATH = os.path.join(_PKG, "lib", "libdllama_b200_layers.so")
 
 DL_MAX_PEERS = 8
-EPI_STORE, EPI_QKV_ROPE, EPI_SILU_MUL = 0, 1, 2
+EPI_STORE, EPI_QKV_ROPE, EPI_SILU_MUL, EPI_DENSE = 0, 1, 2, 3
 
 
 class NativeLibraryError(RuntimeError):
@@ -56,6 +56,10 @@ class DlEpilogue(C.Structure):
         ("out_mcap", C.c_int),
         ("act_gelu", C.c_int),
         ("ll", C.c_int),
+        ("dense_op", C.c_int),
+        ("dense_param", C.c_float),
+        ("dense_aux", C.c_void_p),
+        ("dense_aux_ld", C.c_longlong),
     ]
 
 
@@ -284,12 +288,18 @@ def layers_lib():
     L.dl_latent_attention.argtypes = [C.POINTER(DlLatentAttnArgs), i32, vp]
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
+    L.dl_wh_bytes.restype = i64
+    L.dl_wh_bytes.argtypes = [i32, i32]
+    L.dl_wh_from_dense.argtypes = [vp, i32, i32, i64, vp, vp]
+    L.dl_xh_from_rows.argtypes = [vp, i64, i32, i32, i32, vp, vp]
+    L.dl_gemm_wh_tc.argtypes = [vp, i32, i32, vp, i32, i32, C.POINTER(DlEpilogue), i32, i32, vp]
     L.dl_sample_rows.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, vp]
     L.dl_argmax.argtypes = [vp, i32, i32, i32, vp, vp, i32, vp, u32, u32, vp, vp, i32, vp, i32, vp]
     L.dl_argmax_scratch_bytes.restype = i64
     L.dl_argmax_scratch_bytes.argtypes = [i32]
     for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention",
-                 "dl_mamba_conv", "dl_mamba_scan", "dl_sample_rows", "dl_argmax"):
+                 "dl_mamba_conv", "dl_mamba_scan", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
+                 "dl_gemm_wh_tc"):
         getattr(L, name).restype = i32
     _layers = L
     return L

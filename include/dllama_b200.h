@@ -21,7 +21,10 @@ enum {
     DL_EPI_STORE = 0,     /* f32 store (optionally Q80 round-trip) to 1..8 (peer) buffers + flags  */
     DL_EPI_QKV_ROPE = 1,  /* RoPE on q,k rows; q -> buffer; k,v -> paged KV cache                   */
     DL_EPI_SILU_MUL = 2,  /* rows interleaved (gate,up): act(g)*u -> Q80 activation slabs           */
+    DL_EPI_DENSE = 3,     /* f32 store to dst[0] through one of the DL_DENSE_* element-wise ops      */
 };
+/* element-wise ops on a matmul result (dense-weight models): store, relu(.)^2, aux * sigmoid(.), param * tanh(. / param) */
+enum { DL_DENSE_STORE = 0, DL_DENSE_RELU2 = 1, DL_DENSE_SIGMOID_MUL = 2, DL_DENSE_SOFTCAP = 3 };
 
 typedef struct {
     int kind;
@@ -57,6 +60,11 @@ typedef struct {
     /* DL_EPI_STORE, tensor-parallel partial sums: 1 = dst[] are arrays of {f32 bits, epoch} 8-byte words (LL
      * protocol: no fence, no flags; step_counter / flag_mul / flag_add give the epoch), 0 = plain f32 */
     int ll;
+    /* DL_EPI_DENSE: dst[0][dst_off + m*ld + row] = op(value, dense_aux[m*dense_aux_ld + row], dense_param) */
+    int dense_op;
+    float dense_param;
+    const float* dense_aux;
+    long long dense_aux_ld;
 } DlEpilogue;
 
 /* Fused activation producer for dl_gemv_q40: the kernel itself computes
@@ -301,7 +309,6 @@ int dl_peer_barrier(uint32_t* const* flags_on_peers /*host array*/, uint32_t* my
 /* ==== layer-list models: dense bf16 / f32 weights, latent attention, Mamba-2 ===================
  * Built into libdllama_b200_layers.so (dense.cu, norms.cu, latent_attention.cu, mamba2.cu, plus the shared
  * prep.cu and sampler.cu).  Activations between kernels are f32; `wtype` / `ctype`: 0 = f32, 1 = bf16. */
-enum { DL_DENSE_STORE = 0, DL_DENSE_RELU2 = 1, DL_DENSE_SIGMOID_MUL = 2, DL_DENSE_SOFTCAP = 3 };
 
 /* Y[b][m][n] = epi( sum_k X[b][m][k] * W[b][n][k] ),  b < batch (element strides *_bs).  round_x: the activation
  * operand is rounded to bf16 on load (bf16 mode).  DL_DENSE_SIGMOID_MUL: aux[m][n] * sigmoid(.);
@@ -318,6 +325,12 @@ typedef struct {
 } DlDenseArgs;
 int dl_dense(const DlDenseArgs* args /*host*/, void* stream);
 int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, void* stream);
+/* Tensor-core path of the same product for bf16 weights and many rows: dl_gemm_wh_tc (flags bit 1 = bf16 operands) on
+ * the pre-tiled images these two write.  Weights [N][K] row-major bf16 -> tiles of 128 rows x 128 K in the UMMA K-major
+ * core-matrix image, [ceil(N/128)][ceil(K/128)][32 KB], zero-padded (dl_wh_bytes(N, round_up(K, 128)) bytes).
+ * Activations: columns [0, K) of M f32 rows -> bf16 slabs [ceil(K/128)][ncap/8][2048 B], zero-padded along K. */
+int dl_wh_from_dense(const void* w /*bf16*/, int N, int K, long long ldw, uint8_t* wh, void* stream);
+int dl_xh_from_rows(const float* x, long long ldx, int M, int K, int ncap, uint8_t* xh, void* stream);
 
 /* y[m] (+)= v / sqrt(mean(v^2) + eps) * scale per group of dim/groups values; v = x[rows ? rows[m] : m] (* silu(gate));
  * scale = w, 1 + w (plus_one) or 1 (w NULL).  In place (y == x) is allowed without `accumulate`. */

@@ -101,6 +101,34 @@ def test_dense_products_shapes_and_epilogues(wdtype):
                 assert float(y[M:].max()) == -3.0 and float(y[:, N:].max()) == -3.0       # nothing written outside
 
 
+def test_dense_products_on_the_tensor_cores():
+    """bf16 operands through the tcgen05 GEMM on pre-tiled images: sizes that are no multiples of the 128 x 128 tiles,
+    row counts around the 256-row activation tile, every element-wise op."""
+    from dllama_b200.ops import layers as L
+    g = torch.Generator().manual_seed(8)
+    for (M, N, K) in [(33, 130, 200), (256, 128, 128), (257, 384, 72), (700, 257, 640)]:
+        w = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
+        x = torch.randn(M + 1, K + 5, generator=g).cuda()[:, :K]
+        aux = torch.randn(M, N, generator=g).cuda()
+        ncap = (M + 7) // 8 * 8
+        wh = L.make_wh(w)
+        xh = torch.zeros(L.xh_bytes(K, ncap), dtype=torch.uint8, device="cuda")
+        L.xh_from_rows(x, M, K, ncap, xh)
+        ref = x[:M].bfloat16().double() @ w.double().T
+        for epi, fn in [(L.DENSE_STORE, lambda a: a), (L.DENSE_RELU2, lambda a: a.clamp(min=0) ** 2),
+                        (L.DENSE_SIGMOID_MUL, lambda a: aux.double() * torch.sigmoid(a)),
+                        (L.DENSE_SOFTCAP, lambda a: 9.0 * torch.tanh(a / 9.0))]:
+            y = torch.full((M + 1, N + 3), -3.0, device="cuda")
+            L.dense_tc(wh, N, K, xh, ncap, y, M, epi=epi, aux=aux if epi == L.DENSE_SIGMOID_MUL else None, param=9.0)
+            want = fn(ref)
+            assert torch.allclose(y[:M, :N].double(), want, rtol=2e-4, atol=2e-4 * float(want.abs().max())), (M, N, K, epi)
+            assert float(y[M:].max()) == -3.0 and float(y[:, N:].max()) == -3.0
+        y2 = torch.zeros(M, N, device="cuda")
+        L.dense(w, x, y2, M, True)                                   # the two paths agree to accumulation order
+        L.dense_tc(wh, N, K, xh, ncap, y, M)
+        assert torch.allclose(y[:M, :N], y2, rtol=1e-4, atol=1e-4 * float(ref.abs().max()))
+
+
 def test_dense_per_head_products():
     from dllama_b200.ops import layers as L
     g = torch.Generator().manual_seed(2)
@@ -224,6 +252,7 @@ def _run_mixer(eng, h, portions, slot):
     for n in portions:
         eng.set_batch([0] * n, list(range(at, at + n)), [slot] * n, [])
         eng.hn[:n] = h[at:at + n]
+        eng.begin_sublayer()
         eng.layers[0].mixer.forward(eng.hn, eng.y, n)
         out.append(eng.y[:n].clone())
         at += n
