@@ -48,6 +48,11 @@ def parse_args():
     ap.add_argument("--long-prompt", type=int, default=4096, help="also measure the TTFT of one long prompt run as a single batch on fp16-expanded weights (key ttft_long; 0 = skip)")
     ap.add_argument("--model-dir", default=os.environ.get("DLLAMA_MODEL_DIR", "/dev/shm"))
     ap.add_argument("--nthreads", type=int, default=0, help="reference arm: threads per node (0 = auto)")
+    ap.add_argument("--layered", default="", help="instead of the headline benchmark: prefill and decode throughput of the "
+                    "layer-list design (Ribivik: Mamba-2 + latent attention, bf16) beside a Q40 Llama of equal width, "
+                    "feed-forward size and depth, at these sizes (comma separated: w2048, w4096); prints one JSON line")
+    ap.add_argument("--layered-layers", type=int, default=4, help="--layered: layers of both models")
+    ap.add_argument("--layered-prompt", type=int, default=2048, help="--layered: prompt length (one batch)")
     return ap.parse_args()
 
 
@@ -392,6 +397,125 @@ def run_nccl_cublas(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------------
+# --layered: the layer-list design beside the closest existing model, at sizes that resemble a real model's layers
+# --------------------------------------------------------------------------------------------------
+LAYERED_SIZES = {
+    # width, ff, attention heads (head size 128 for the Llama arm), Mamba-2 heads x vdim = 2 x width
+    "w2048": dict(width=2048, ff=8192, heads=16, q_rank=1536, kv_rank=512, m_heads=64, m_groups=8),
+    "w4096": dict(width=4096, ff=14336, heads=32, q_rank=1536, kv_rank=512, m_heads=128, m_groups=8),
+}
+
+
+def layered_config(sz: dict, n_layers: int, vocab: int) -> dict:
+    import math
+    layers = []
+    for i in range(n_layers):
+        if i % 2 == 0:
+            layers.append({"type": "mamba2", "mlp": None,
+                           "mixer": {"heads": sz["m_heads"], "vdim": 64, "state": 128, "groups": sz["m_groups"], "conv": 4,
+                                     "norm_groups": sz["m_groups"]}})
+        else:
+            mixer = {"heads": sz["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": sz["q_rank"],
+                     "kv_rank": sz["kv_rank"], "scale": 1.0 / math.sqrt(192.0), "rot": {"base": 10000.0, "dims": 64}}
+            if i >= 5:
+                mixer["kv_from"] = 3
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": sz["ff"]}})
+    return {"architecture": "Ribivik", "width": sz["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": layers}
+
+
+def _time_ms(fn, warmup: int, steps: int):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1) / steps
+
+
+def _bench_engine(eng, vocab: int, T: int, users: int, warmup: int, steps: int) -> dict:
+    """Prompt of T tokens as one batch (tok/s), then single-stream and `users`-way decode at that context (tok/s).
+    Every call re-feeds the prompt from position 0 into the same slot / continues the same sequences, so the timed
+    work is the steady state; the weights of every arm exceed the 126 MB L2."""
+    import numpy as np
+    import torch
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(1, vocab, T).tolist()
+    slots = [eng.alloc_slot() for _ in range(users)]
+    pos_all = list(range(T))
+
+    def prefill():
+        eng.forward(prompt, pos_all, [slots[0]] * T, logits_from=T - 1)
+
+    out = {"prefill_ms": _time_ms(prefill, max(3, warmup // 2), max(3, steps // 8))}
+    out["prefill_tok_s"] = T / out["prefill_ms"] * 1e3
+    for s in slots[1:]:
+        eng.forward(prompt, pos_all, [s] * T, logits_from=T - 1)
+    pos = [T] * users
+    tok = [1] * users
+
+    def decode(n):
+        def f():
+            nonlocal tok
+            tok = eng.decode_step_greedy(tok[:n], pos[:n], slots[:n])
+            tok = tok + [1] * (users - n)
+            for i in range(n):
+                pos[i] += 1
+        return f
+
+    out["decode1_ms"] = _time_ms(decode(1), warmup, steps)
+    out["decode1_tok_s"] = 1e3 / out["decode1_ms"]
+    out[f"decode{users}_ms"] = _time_ms(decode(users), warmup, steps)
+    out[f"decode{users}_tok_s"] = users * 1e3 / out[f"decode{users}_ms"]
+    return out
+
+
+def run_layered(args):
+    import torch
+    from dllama_b200.formats import mfile
+    from dllama_b200.models import registry
+    from dllama_b200.models.layered import write_random_model
+    from dllama_b200.models.llama import LlamaEngine
+    from dllama_b200.ops import quant
+    torch.cuda.set_device(0)
+    T, users, vocab, nl = args.layered_prompt, min(args.users, 32) or 32, 32768, args.layered_layers
+    ctx = T + 4 * (args.steps + args.warmup) + 64
+    sampler = ClockSampler(0)
+    sampler.start()
+    rows = {}
+    for name in [s for s in args.layered.split(",") if s]:
+        sz = LAYERED_SIZES[name]
+        d = os.path.join(args.model_dir, f"dllama_b200_layered_{name}_l{nl}")
+        if not os.path.exists(os.path.join(d, "model.safetensors")):
+            write_random_model(d, layered_config(sz, nl, vocab), seed=1)
+        eng = registry.engine_for_dir(d, max_rows=max(T, users), n_slots=users, max_seq_len=ctx, dtype="bfloat16")
+        r = _bench_engine(eng, vocab, T, users, args.warmup, args.steps)
+        r["weight_gb"] = eng.weight_bytes() / 1e9
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+        shape = dict(dim=sz["width"], hidden_dim=sz["ff"], n_layers=nl, n_heads=sz["heads"], n_kv_heads=8, vocab_size=vocab,
+                     max_seq_len=8192, rope_theta=10000, rope=None)
+        path = os.path.join(args.model_dir, f"dllama_b200_llama_{name}_l{nl}_q40.m")
+        if not os.path.exists(path):
+            mfile.write_random_model(path, shape, quant.Q40, seed=1)
+        le = LlamaEngine(path, max_rows=max(T, users), n_slots=users, max_seq_len=ctx)
+        q = _bench_engine(le, vocab, T, users, args.warmup, args.steps)
+        q["weight_gb"] = le.weight_bytes() / 1e9
+        le.close()
+        del le
+        torch.cuda.empty_cache()
+        rows[name] = {"ribivik_bf16": r, "llama_q40": q}
+    print(json.dumps({"layered": rows, "layers": nl, "prompt": T, "users": users, "steps": args.steps, "warmup": args.warmup,
+                      "data": "synthetic", "clocks": sampler.stop()}), flush=True)
+
+
 def run_reference(args):
     from baseline.reference_arm import run_reference_arm
     print(json.dumps(run_reference_arm(args, METRIC)), flush=True)
@@ -416,7 +540,9 @@ if __name__ == "__main__":
             if int(os.environ.get("RANK", "0")) == 0:
                 print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}), flush=True)
         sys.exit(0)
-    if a.impl == "nccl_cublas":
+    if a.layered:
+        run_layered(a)
+    elif a.impl == "nccl_cublas":
         run_nccl_cublas(a)
     else:
         run_b200(a)

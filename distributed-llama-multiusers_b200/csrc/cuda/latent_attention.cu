@@ -169,3 +169,293 @@ extern "C" int dl_latent_attention(const DlLatentAttnArgs* args, int M, void* st
     LAYER_CHECK_LAUNCH("dl_latent_attention");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Tensor-core variant (bf16 cache): a CTA owns a tile of up to LQ_ROWS "query rows x heads" of one sequence
+// (consecutive positions x all heads: every head reads the same cache lines, so heads stack on the M dimension of
+// the MMA) and walks the sequence's pages.  Per page (32 tokens):
+//     S[32 x 32]  = Q[32 x D] . C[32 x D]^T        each of the NJ column-warps takes D / NJ of the K dimension;
+//                                                  the partial products meet in shared memory
+//     softmax     (f32, online; every warp of a row tile redoes the cheap 16 x 32 part)
+//     O[32 x R]  += P[32 x 32] . C[32 x R]         each column-warp owns R / NJ output columns in registers
+// Warps: NI row tiles of 16 x NJ column-warps.  mma.sync m16n8k16 bf16; B fragments of P.C by ldmatrix.trans.
+// With `n_splits` > 1 (decode: few tiles, long contexts) CTAs along grid.y take page ranges and leave unnormalised
+// partial sums that latent_merge_kernel combines.
+// ------------------------------------------------------------------------------------------------
+#define LQ_ROWS 32
+#define LQ_NJ 4
+#define LQ_NI (LQ_ROWS / 16)
+#define LQ_THREADS (32 * LQ_NJ * LQ_NI)
+#define LQ_SP_LD 33
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// NT: n-tiles (8 columns) of O per column-warp; the kernel covers rank <= NT * 8 * LQ_NJ
+template <int NT>
+__global__ void __launch_bounds__(LQ_THREADS) latent_attention_mma_kernel(DlLatentAttnArgs a, DlLatentTiles tl) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    const int H = a.n_heads, R = a.rank, D = a.rank + a.rot;
+    const int Dp = tl.d_pad, LD = Dp + 8;                 // row stride in bf16: 16-byte multiple, conflict-free
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smraw);         // [LQ_ROWS][LD]
+    __nv_bfloat16* c_s = q_s + LQ_ROWS * LD;                              // [32][LD]
+    float* sp = reinterpret_cast<float*>(c_s + 32 * LD);                  // [LQ_NI][LQ_NJ][16][LQ_SP_LD]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wi = warp / LQ_NJ, wj = warp % LQ_NJ, g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int* trows = tl.tile_rows + (size_t)tile * tl.rq;
+    const int row_first = trows[0];
+    const int slot = a.slot[row_first], pos0 = a.pos[row_first];
+    int n_rows = 0;
+    for (int i = 0; i < tl.rq; ++i) n_rows += trows[i] >= 0 ? 1 : 0;
+    const int m_live = n_rows * H;                        // stacked rows: mr = rq * H + h
+    // ---- stage Q (absorbed part | rotated part | zero padding) as bf16 ----
+    for (int i = tid; i < LQ_ROWS * Dp; i += LQ_THREADS) {
+        const int mr = i / Dp, d = i % Dp;
+        float v = 0.f;
+        if (mr < m_live && d < D) {
+            const int row = trows[mr / H], h = mr % H;
+            v = d < R ? a.q_lat[((size_t)row * H + h) * R + d]
+                      : a.q[(size_t)row * a.ldq + (size_t)h * a.q_head_stride + a.q_rot_offset + (d - R)];
+        }
+        q_s[mr * LD + d] = __float2bfloat16_rn(v);
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // rows g and g + 8 of this warp's row tile
+    const int mr0 = wi * 16 + g, mr1 = mr0 + 8;
+    const int qpos0 = pos0 + (mr0 < m_live ? mr0 / H : 0), qpos1 = pos0 + (mr1 < m_live ? mr1 / H : 0);
+    const bool live0 = mr0 < m_live, live1 = mr1 < m_live;
+    const int last_pos = pos0 + n_rows - 1;
+    const int n_pages = last_pos / 32 + 1;
+    const int per = (n_pages + tl.n_splits - 1) / tl.n_splits;
+    const int p_begin = split * per, p_end = min(n_pages, p_begin + per);
+    const int ks_per = Dp / LQ_NJ / 16;                  // k steps of this warp's share of D
+    const int ocol0 = wj * NT * 8;                       // this warp's output columns
+    for (int pg = p_begin; pg < p_end; ++pg) {
+        __syncthreads();                                  // q_s staged; previous page's tile and partial scores consumed
+        const int page = a.block_table[(size_t)slot * a.max_pages + pg];
+        const __nv_bfloat16* src = (const __nv_bfloat16*)a.cache + (size_t)page * 32 * D;
+        const int valid = min(32, last_pos + 1 - pg * 32);
+        const int dv = D >> 3, dpv = Dp >> 3;             // 16-byte chunks per line
+        for (int i = tid; i < 32 * dpv; i += LQ_THREADS) {
+            const int j = i / dpv, c = i % dpv;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (j < valid && c < dv) v = *reinterpret_cast<const uint4*>(src + (size_t)j * D + c * 8);
+            *reinterpret_cast<uint4*>(c_s + j * LD + c * 8) = v;
+        }
+        __syncthreads();
+        // ---- partial scores over this warp's share of D ----
+        float s[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int ks = 0; ks < ks_per; ++ks) {
+            const int k0 = (wj * ks_per + ks) * 16;
+            uint32_t af[4];
+            const __nv_bfloat16* qa = q_s + (wi * 16 + g) * LD + k0 + 2 * t;
+            af[0] = *reinterpret_cast<const uint32_t*>(qa);
+            af[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD);
+            af[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
+            af[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + 8);
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const __nv_bfloat16* cb = c_s + (n * 8 + g) * LD + k0 + 2 * t;
+                mma_bf16(s[n], af, *reinterpret_cast<const uint32_t*>(cb), *reinterpret_cast<const uint32_t*>(cb + 8));
+            }
+        }
+        float* my_sp = sp + ((wi * LQ_NJ + wj) * 16) * LQ_SP_LD;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            my_sp[g * LQ_SP_LD + n * 8 + 2 * t] = s[n][0];
+            my_sp[g * LQ_SP_LD + n * 8 + 2 * t + 1] = s[n][1];
+            my_sp[(g + 8) * LQ_SP_LD + n * 8 + 2 * t] = s[n][2];
+            my_sp[(g + 8) * LQ_SP_LD + n * 8 + 2 * t + 1] = s[n][3];
+        }
+        __syncthreads();
+        // ---- softmax of rows g, g + 8; this lane's tokens: 2t, 2t+1, 2t+8, 2t+9, 2t+16, ... (the A fragment of P.C) ----
+        float p0[8], p1[8];
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int col = (e >> 1) * 8 + 2 * t + (e & 1);
+            float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < LQ_NJ; ++j) {
+                const float* q = sp + ((wi * LQ_NJ + j) * 16) * LQ_SP_LD;
+                v0 += q[g * LQ_SP_LD + col];
+                v1 += q[(g + 8) * LQ_SP_LD + col];
+            }
+            const int tok = pg * 32 + col;
+            p0[e] = (live0 && tok <= qpos0) ? v0 * a.scale : -INFINITY;
+            p1[e] = (live1 && tok <= qpos1) ? v1 * a.scale : -INFINITY;
+            mx0 = fmaxf(mx0, p0[e]);
+            mx1 = fmaxf(mx1, p1[e]);
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float al0 = mn0 == -INFINITY ? 1.f : expf(m_run[0] - mn0), al1 = mn1 == -INFINITY ? 1.f : expf(m_run[1] - mn1);
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            p0[e] = mn0 == -INFINITY ? 0.f : expf(p0[e] - mn0);
+            p1[e] = mn1 == -INFINITY ? 0.f : expf(p1[e] - mn1);
+            sum0 += p0[e];
+            sum1 += p1[e];
+        }
+        m_run[0] = mn0; m_run[1] = mn1;
+        l_run[0] = l_run[0] * al0 + sum0;                 // per-lane share of the row sum; the 4 lanes of a row meet at the end
+        l_run[1] = l_run[1] * al1 + sum1;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
+        // ---- O += P . C over this warp's columns: two k steps of 16 tokens ----
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t af[4];
+            af[0] = pack_bf16(p0[4 * ks], p0[4 * ks + 1]);
+            af[1] = pack_bf16(p1[4 * ks], p1[4 * ks + 1]);
+            af[2] = pack_bf16(p0[4 * ks + 2], p0[4 * ks + 3]);
+            af[3] = pack_bf16(p1[4 * ks + 2], p1[4 * ks + 3]);
+#pragma unroll
+            for (int n = 0; n < NT; n += 2) {
+                // four 8 x 8 blocks: tokens ks*16 + {0..7, 8..15} x columns {n*8.., (n+1)*8..}; lane supplies one row address
+                const int mat = lane >> 3, rr = lane & 7;
+                const __nv_bfloat16* addr = c_s + (ks * 16 + (mat & 1) * 8 + rr) * LD + ocol0 + (n + (mat >> 1)) * 8;
+                uint32_t b0, b1, b2, b3;
+                const uint32_t sa = (uint32_t)__cvta_generic_to_shared(addr);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(sa));
+                mma_bf16(o[n], af, b0, b1);
+                mma_bf16(o[n + 1], af, b2, b3);
+            }
+        }
+    }
+    // ---- finish: row sums across the 4 lanes of a row, then store (normalised, or partial for the merge) ----
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1); l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1); l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+    if (tl.n_splits == 1) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int mr = half ? mr1 : mr0;
+            if (mr >= m_live) continue;
+            const int row = trows[mr / H], h = mr % H;
+            const float inv = 1.f / l_run[half];
+            float* dst = a.out + ((size_t)row * H + h) * R;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int col = ocol0 + n * 8 + 2 * t;
+                if (col < R) dst[col] = o[n][2 * half] * inv;
+                if (col + 1 < R) dst[col + 1] = o[n][2 * half + 1] * inv;
+            }
+        }
+    } else {
+        // partial[tile][split][mr][rpad + 2]: unnormalised sums, then running maximum and row sum
+        const int rpad = NT * 8 * LQ_NJ;
+        float* base = tl.partial + (((size_t)tile * tl.n_splits + split) * LQ_ROWS) * (rpad + 2);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int mr = half ? mr1 : mr0;
+            float* dst = base + (size_t)mr * (rpad + 2);
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const int col = ocol0 + n * 8 + 2 * t;
+                dst[col] = o[n][2 * half];
+                dst[col + 1] = o[n][2 * half + 1];
+            }
+            if (wj == 0 && t == 0) { dst[rpad] = m_run[half]; dst[rpad + 1] = l_run[half]; }
+        }
+    }
+}
+
+// out[row][h][:] = sum_s w_s O_s / sum_s w_s l_s,  w_s = exp(m_s - max_s m_s); one CTA per (tile, stacked row)
+__global__ void __launch_bounds__(128) latent_merge_kernel(DlLatentAttnArgs a, DlLatentTiles tl, int rpad) {
+    const int tile = blockIdx.x, mr = blockIdx.y, H = a.n_heads, R = a.rank;
+    const int* trows = tl.tile_rows + (size_t)tile * tl.rq;
+    if (mr / H >= tl.rq) return;
+    const int row = trows[mr / H], h = mr % H;
+    if (row < 0) return;
+    const float* base = tl.partial + ((size_t)tile * tl.n_splits * LQ_ROWS + mr) * (rpad + 2);
+    const size_t sstride = (size_t)LQ_ROWS * (rpad + 2);
+    float mx = -INFINITY;
+    for (int s = 0; s < tl.n_splits; ++s) mx = fmaxf(mx, base[s * sstride + rpad]);
+    float den = 0.f;
+    for (int s = 0; s < tl.n_splits; ++s) {
+        const float m = base[s * sstride + rpad];
+        if (m != -INFINITY) den += expf(m - mx) * base[s * sstride + rpad + 1];
+    }
+    for (int d = threadIdx.x; d < R; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < tl.n_splits; ++s) {
+            const float m = base[s * sstride + rpad];
+            if (m != -INFINITY) acc = fmaf(expf(m - mx), base[s * sstride + d], acc);
+        }
+        a.out[((size_t)row * H + h) * R + d] = acc / den;
+    }
+}
+
+extern "C" int dl_latent_tc_rpad(int rank) {
+    const int unit = 8 * LQ_NJ;
+    for (int nt = 2; nt <= 16; nt *= 2)
+        if (rank <= nt * unit) return nt * unit;
+    return -1;
+}
+extern "C" long long dl_latent_tc_partial_floats(int n_tiles, int n_splits, int rank) {
+    const int rpad = dl_latent_tc_rpad(rank);
+    return rpad < 0 ? -1 : (long long)n_tiles * n_splits * LQ_ROWS * (rpad + 2);
+}
+
+// 0 if these sizes run on the tensor-core kernel (bf16 cache, heads stacked into 32 rows, 16-byte cache lines)
+extern "C" int dl_latent_attention_tc_supported(int n_heads, int rank, int rot, int ctype, int rq) {
+    if (ctype != DL_T_BF16 || n_heads < 1 || rq < 1 || rq * n_heads > LQ_ROWS) return -1;
+    if ((rank + rot) % 8 != 0 || dl_latent_tc_rpad(rank) < 0) return -1;
+    return 0;
+}
+
+template <int NT>
+static int launch_latent_mma(const DlLatentAttnArgs& a, const DlLatentTiles& tl, size_t smem, cudaStream_t st) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { dl_set_error("dl_latent_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
+    latent_attention_mma_kernel<NT><<<dim3(tl.n_tiles, tl.n_splits), LQ_THREADS, smem, st>>>(a, tl);
+    return 0;
+}
+
+extern "C" int dl_latent_attention_tc(const DlLatentAttnArgs* args, const DlLatentTiles* tiles, void* stream) {
+    const DlLatentAttnArgs& a = *args;
+    DlLatentTiles tl = *tiles;
+    if (a.page_size != 32) { dl_set_error("dl_latent_attention_tc: page size must be 32"); return -1; }
+    if (dl_latent_attention_tc_supported(a.n_heads, a.rank, a.rot, a.ctype, tl.rq) != 0) {
+        dl_set_error("dl_latent_attention_tc: %d heads x %d rows, rank %d + %d not supported", a.n_heads, tl.rq, a.rank, a.rot);
+        return -1;
+    }
+    if (tl.n_tiles < 1 || tl.n_splits < 1 || (tl.n_splits > 1 && tl.partial == nullptr)) { dl_set_error("dl_latent_attention_tc: bad tiling"); return -1; }
+    const int rpad = dl_latent_tc_rpad(a.rank);
+    const int unit = 16 * LQ_NJ;
+    int dp = (a.rank + a.rot + unit - 1) / unit * unit;
+    if (dp < rpad) dp = rpad;                             // P.C reads `rpad` columns of every staged line
+    tl.d_pad = dp;
+    const size_t smem = (size_t)(LQ_ROWS + 32) * (dp + 8) * 2 + (size_t)LQ_NI * LQ_NJ * 16 * LQ_SP_LD * 4;
+    if (smem > 227 * 1024) { dl_set_error("dl_latent_attention_tc: rank %d needs %zu bytes of shared memory", a.rank, smem); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+    switch (rpad / (8 * LQ_NJ)) {
+        case 2: rc = launch_latent_mma<2>(a, tl, smem, st); break;
+        case 4: rc = launch_latent_mma<4>(a, tl, smem, st); break;
+        case 8: rc = launch_latent_mma<8>(a, tl, smem, st); break;
+        default: rc = launch_latent_mma<16>(a, tl, smem, st); break;
+    }
+    if (rc != 0) return rc;
+    LAYER_CHECK_LAUNCH("dl_latent_attention_tc");
+    if (tl.n_splits > 1) {
+        latent_merge_kernel<<<dim3(tl.n_tiles, tl.rq * a.n_heads), 128, 0, st>>>(a, tl, rpad);
+        LAYER_CHECK_LAUNCH("dl_latent_attention_tc merge");
+    }
+    return 0;
+}

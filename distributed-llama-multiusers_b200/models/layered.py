@@ -172,7 +172,8 @@ class LatentAttentionMixer:
             L.latent_kv_write(kv, M, self.dkv_norm, e.cfg.norm_eps, r, dr, self.rope_dims, self.freqs, e.pos, e.slot,
                               e.block_table, self.cache)
         e.mm_heads(self.w_uk_t, q, q_lat, M, hd, r)
-        L.latent_attention(q_lat, q, hd, dn, o_lat, M, H, r, dr, self.scale, e.pos, e.slot, e.block_table, self.cache)
+        L.latent_attention(q_lat, q, hd, dn, o_lat, M, H, r, dr, self.scale, e.pos, e.slot, e.block_table, self.cache,
+                           tiles=e.latent_tiles(self))
         e.mm_heads(self.w_uv, o_lat, o, M, r, dv)
         e.mm(self.w_g, h, og, M, epi=L.DENSE_SIGMOID_MUL, aux=o, src="h")
         e.mm(self.w_o, og, y, M)
@@ -308,6 +309,19 @@ class LayerListEngine:
         mixers = [l.mixer for l in self.layers]
         for mx in mixers:
             mx.bind(mixers)
+        # latent attention on the tensor cores (bf16 caches): rows of a sequence are tiled so that rows x heads <= 32
+        att = [mx for mx in mixers if isinstance(mx, LatentAttentionMixer)]
+        self.attn_rq = 0
+        if att and self.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0":
+            rq = max(1, min(16, L.LATENT_TC_ROWS // max(mx.H for mx in att)))
+            if any(L.latent_tc_supported(mx.H, mx.rank, mx.dr, self.wdtype, rq) for mx in att):
+                self.attn_rq = rq
+        self.n_sms = L.sm_count()
+        self._n_tiles = self._n_splits = 0
+        self._attn_partial = None
+        if self.attn_rq:
+            rmax = max(mx.rank for mx in att)
+            self._attn_partial = torch.zeros(L.latent_tc_partial_floats(3 * self.n_sms, 1, rmax), dtype=torch.float32, device=dev)
         # scratch: one f32 buffer per name, as wide as the widest user
         widths: Dict[str, int] = {}
         for l in self.layers:
@@ -331,13 +345,16 @@ class LayerListEngine:
         # batch descriptor (one pinned -> device copy per step):
         #   tokens | pos | slot | row_seq | seq_rows | logit_rows   [R] each, then seq_start [S+1] | seq_slot [S] | seq_pos0 [S]
         S = self.n_slots
-        self._desc_len = 6 * R + 3 * S + 1
+        self._tiles_off = 6 * R + 3 * S + 1                  # then tile_rows [n_tiles][rq] of the attention kernel
+        self._desc_len = self._tiles_off + R + 16 * S
+        self.tile_rows = None
         self.h_desc = torch.zeros(self._desc_len, dtype=torch.int32).pin_memory()
         self.desc = torch.zeros(self._desc_len, dtype=torch.int32, device=dev)
         d = self.desc
         self.tokens, self.pos, self.slot, self.row_seq, self.seq_rows, self.logit_rows = (d[i * R:(i + 1) * R] for i in range(6))
         o = 6 * R
         self.seq_start, self.seq_slot, self.seq_pos0 = d[o:o + S + 1], d[o + S + 1:o + 2 * S + 1], d[o + 2 * S + 1:o + 3 * S + 1]
+        self.tile_rows = d[self._tiles_off:]
         self.mamba_batch = L.mamba_batch(self.pos, self.row_seq, self.seq_start, self.seq_rows, self.seq_slot, self.seq_pos0)
         self.n_seq = 0
         self.block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32, device=dev)
@@ -387,6 +404,13 @@ class LayerListEngine:
         for h in range(w.t.shape[0]):
             L.xh_from_rows(x[:, h * x_head_stride:], M, w.K, self.ncap, self._xh["tmp"])
             L.dense_tc(w.wh[h], w.N, w.K, self._xh["tmp"], self.ncap, y[:, h * y_head_stride:], M)
+
+    def latent_tiles(self, mx):
+        """The row tiling of this batch for the tensor-core attention kernel, or None where the per-row kernel runs."""
+        L = self.L
+        if not self.attn_rq or not L.latent_tc_supported(mx.H, mx.rank, mx.dr, self.wdtype, self.attn_rq):
+            return None
+        return (self.tile_rows, self._n_tiles, self.attn_rq, self._n_splits, self._attn_partial)
 
     def begin_sublayer(self):
         self._xh_h_ready = False
@@ -449,6 +473,19 @@ class LayerListEngine:
             self.pages.ensure(s, p0 + len(rows))
             self._slot_len[s] = p0 + len(rows)
         hd[o + len(by_slot)] = at
+        if self.attn_rq:
+            # attention tiles: up to rq rows of one sequence at consecutive positions; few tiles (decoding) share their
+            # pages among several CTAs
+            rq, to, nt, pages = self.attn_rq, self._tiles_off, 0, 1
+            for s, rows in by_slot.items():
+                for i in range(0, len(rows), rq):
+                    part = rows[i:i + rq]
+                    hd[to + nt * rq:to + nt * rq + len(part)] = part
+                    hd[to + nt * rq + len(part):to + (nt + 1) * rq] = -1
+                    nt += 1
+                pages = max(pages, (int(self._slot_len[s]) + PAGE - 1) // PAGE)
+            self._n_tiles = nt
+            self._n_splits = 1 if nt >= self.n_sms else max(1, min(32, (2 * self.n_sms) // nt, pages // 2))
         nl = len(logit_rows)
         hd[5 * R:5 * R + nl] = logit_rows
         if self.pages.dirty:

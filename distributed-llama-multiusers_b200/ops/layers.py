@@ -11,7 +11,7 @@ import torch
 
 from . import lib
 from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
-                  DlEpilogue, DlLatentAttnArgs, DlLatentKvArgs, DlMambaBatch, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
+                  DlEpilogue, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
 
@@ -144,9 +144,23 @@ def rope_rows(x: torch.Tensor, M: int, n_heads: int, head_stride: int, offset: i
     lib.count_launch()
 
 
+LATENT_TC_ROWS = 32          # stacked (query row x head) rows of one tile of the tensor-core kernel
+
+
+def latent_tc_supported(n_heads: int, rank: int, rot: int, cache_dtype, rq: int) -> bool:
+    ctype = T_BF16 if cache_dtype == torch.bfloat16 else T_F32
+    return layers_lib().dl_latent_attention_tc_supported(n_heads, rank, rot, ctype, rq) == 0
+
+
+def latent_tc_partial_floats(n_tiles: int, n_splits: int, rank: int) -> int:
+    return int(layers_lib().dl_latent_tc_partial_floats(n_tiles, n_splits, rank))
+
+
 def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_head_stride: int, q_rot_offset: int, out: torch.Tensor,
                      M: int, n_heads: int, rank: int, rot: int, scale: float, pos, slot, block_table: torch.Tensor,
-                     cache: torch.Tensor):
+                     cache: torch.Tensor, tiles=None):
+    """tiles = (tile_rows int32 [n_tiles][rq], n_tiles, rq, n_splits, partial f32 or None): the tensor-core kernel over
+    row tiles of one sequence each (bf16 cache); None: the per-row kernel (any cache type)."""
     a = DlLatentAttnArgs()
     a.q_lat, a.q, a.ldq = q_lat.data_ptr(), q.data_ptr(), q.stride(0)
     a.q_head_stride, a.q_rot_offset, a.out = q_head_stride, q_rot_offset, out.data_ptr()
@@ -154,6 +168,12 @@ def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_head_stride: int, q
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
     a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
     a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    if tiles is not None:
+        t = DlLatentTiles()
+        t.tile_rows, t.n_tiles, t.rq, t.n_splits, t.partial = tiles[0].data_ptr(), tiles[1], tiles[2], tiles[3], _p(tiles[4])
+        check_layers(layers_lib().dl_latent_attention_tc(a, t, _stream()), "dl_latent_attention_tc")
+        lib.count_launch(2 if tiles[3] > 1 else 1)
+        return
     check_layers(layers_lib().dl_latent_attention(a, M, _stream()), "dl_latent_attention")
     lib.count_launch()
 

@@ -251,6 +251,12 @@ class DlLatentAttnArgs(C.Structure):
                 ("cache", C.c_void_p), ("ctype", C.c_int)]
 
 
+class DlLatentTiles(C.Structure):
+    """Mirror of ``DlLatentTiles``."""
+    _fields_ = [("tile_rows", C.c_void_p), ("n_tiles", C.c_int), ("rq", C.c_int), ("n_splits", C.c_int),
+                ("partial", C.c_void_p), ("d_pad", C.c_int)]
+
+
 class DlMambaBatch(C.Structure):
     """Mirror of ``DlMambaBatch``."""
     _fields_ = [("pos", C.c_void_p), ("row_seq", C.c_void_p), ("seq_start", C.c_void_p), ("seq_rows", C.c_void_p),
@@ -286,6 +292,11 @@ def layers_lib():
     L.dl_latent_kv_write.argtypes = [C.POINTER(DlLatentKvArgs), i32, vp]
     L.dl_rope_rows.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
     L.dl_latent_attention.argtypes = [C.POINTER(DlLatentAttnArgs), i32, vp]
+    L.dl_latent_attention_tc.argtypes = [C.POINTER(DlLatentAttnArgs), C.POINTER(DlLatentTiles), vp]
+    L.dl_latent_attention_tc_supported.argtypes = [i32, i32, i32, i32, i32]
+    L.dl_latent_attention_tc_supported.restype = i32
+    L.dl_latent_tc_partial_floats.argtypes = [i32, i32, i32]
+    L.dl_latent_tc_partial_floats.restype = i64
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
     L.dl_wh_bytes.restype = i64
@@ -297,7 +308,7 @@ def layers_lib():
     L.dl_argmax.argtypes = [vp, i32, i32, i32, vp, vp, i32, vp, u32, u32, vp, vp, i32, vp, i32, vp]
     L.dl_argmax_scratch_bytes.restype = i64
     L.dl_argmax_scratch_bytes.argtypes = [i32]
-    for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention",
+    for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention", "dl_latent_attention_tc",
                  "dl_mamba_conv", "dl_mamba_scan", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
                  "dl_gemm_wh_tc"):
         getattr(L, name).restype = i32

@@ -17,6 +17,9 @@ ENV_VARS = {
     "DLLAMA_WH_MIN_ROWS": ("768", "batch size from which the resident fp16 copy is used"),
     "DLLAMA_WH_MIN_ROWS_SCRATCH": ("2048", "same for the scratch mode (expansion per call)"),
     "DLLAMA_PREFILL_TC_MIN_ROWS": ("128", "batch size from which prompt chunks use the tcgen05 attention kernel"),
+    "DLLAMA_LAYERS_TC": ("1", "layer-list models in bf16: 0 = never use the tcgen05 GEMM (every product on the streaming / tiled kernels)"),
+    "DLLAMA_LAYERS_ATTN_TC": ("1", "layer-list models in bf16: 0 = latent attention on the per-row kernel instead of the tensor-core one"),
+    "DLLAMA_LAYERS_TC_MIN_ROWS": ("32", "layer-list models: batch size from which matrix products run on the tcgen05 GEMM"),
     # serving / tensor-parallel control
     "DLLAMA_HOST_SAMPLER": ("0", "1 = sample on the host (reference-exact sampler) instead of the device kernel"),
     "DLLAMA_MAX_WAITING": ("4096", "requests the native server queues before it answers 503"),

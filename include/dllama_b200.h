@@ -376,6 +376,19 @@ typedef struct {
     const void* cache; int ctype;
 } DlLatentAttnArgs;
 int dl_latent_attention(const DlLatentAttnArgs* args /*host*/, int M, void* stream);
+/* Tensor-core variant (bf16 cache).  The batch's rows are grouped on the host into tiles of up to `rq` rows of one
+ * sequence at consecutive positions: tile_rows[n_tiles][rq] holds row indices, -1 where a tile has fewer rows
+ * (rq * n_heads <= 32).  n_splits > 1: CTAs share a tile's pages and `partial` (dl_latent_tc_partial_floats() f32)
+ * holds their unnormalised sums for the merge kernel that follows. */
+typedef struct {
+    const int* tile_rows;
+    int n_tiles, rq, n_splits;
+    float* partial;
+    int d_pad;                                /* set by the library */
+} DlLatentTiles;
+int dl_latent_attention_tc_supported(int n_heads, int rank, int rot, int ctype, int rq);
+long long dl_latent_tc_partial_floats(int n_tiles, int n_splits, int rank);
+int dl_latent_attention_tc(const DlLatentAttnArgs* args /*host*/, const DlLatentTiles* tiles /*host*/, void* stream);
 
 /* batch description for recurrent layers (device arrays): sequence n owns rows seq_rows[seq_start[n] .. seq_start[n+1])
  * in position order, starting at position seq_pos0[n], with its state in slot seq_slot[n]; row_seq / pos are per row */

@@ -218,6 +218,53 @@ def test_latent_attention_sees_exactly_the_keys_up_to_its_position(ctype):
             assert torch.allclose(out.cpu().double().view(H, r)[h], want, atol=2e-5, rtol=1e-4), (qpos, kpos, h)
         if kpos <= qpos:
             assert float(p[kpos]) > 0.9                                        # the test's premise: that key dominates
+        if ctype == torch.bfloat16:
+            # the tensor-core kernel (queries and probabilities rounded to bf16), alone and with the pages split over CTAs
+            rows = torch.tensor([0], dtype=torch.int32, device="cuda")
+            for n_splits in (1, 3):
+                part = torch.zeros(L.latent_tc_partial_floats(1, n_splits, r), device="cuda")
+                out2 = torch.full((1, H * r), 7.0, device="cuda")
+                L.latent_attention(q_lat.reshape(1, H * r).cuda(), q.cuda(), 4 + rot, 4, out2, 1, H, r, rot, 0.5, pos, slot,
+                                   table.cuda(), cache, tiles=(rows, 1, 1, n_splits, part))
+                assert torch.allclose(out2, out, atol=3e-2, rtol=3e-2), (qpos, kpos, n_splits)
+
+
+def test_latent_attention_tiles_of_several_rows_on_the_tensor_cores():
+    """Row tiles of one sequence (rows x heads stacked on the MMA's M dimension), tiles with fewer rows than the tile
+    holds, rows of two sequences in one batch in scrambled order, against the per-row kernel."""
+    from dllama_b200.ops import layers as L
+    g = torch.Generator().manual_seed(16)
+    for H, r, rot, rq in [(3, 40, 8, 10), (16, 512, 64, 2), (5, 96, 16, 6), (32, 64, 32, 1)]:
+        n_pages = 12
+        cache = (torch.randn(n_pages, 32, r + rot, generator=g) * 0.5).to(torch.bfloat16).cuda()
+        table = torch.stack([torch.randperm(n_pages, generator=g)[:6], torch.randperm(n_pages, generator=g)[:6]]).int().cuda()
+        # sequence 0: positions 90..120 (31 rows), sequence 1: positions 0..12; rows interleaved in the batch
+        rows0, rows1 = list(range(0, 62, 2)), list(range(1, 27, 2))
+        M = 62
+        pos = torch.zeros(M, dtype=torch.int32)
+        slot = torch.zeros(M, dtype=torch.int32)
+        pos[rows0], slot[rows0] = torch.arange(90, 121, dtype=torch.int32), 0
+        pos[rows1], slot[rows1] = torch.arange(0, 13, dtype=torch.int32), 1
+        pos[27:62:2], slot[27:62:2] = 0, 1                                       # filler rows, not in any tile
+        hd = 4 + rot
+        q_lat = torch.randn(M, H * r, generator=g).cuda() * 0.3
+        q = torch.randn(M, H * hd, generator=g).cuda() * 0.3
+        want = torch.zeros(M, H * r, device="cuda")
+        L.latent_attention(q_lat, q, hd, 4, want, M, H, r, rot, 0.2, pos.cuda(), slot.cuda(), table, cache)
+        tiles = []
+        for rows in (rows0, rows1):
+            for i in range(0, len(rows), rq):
+                part = rows[i:i + rq]
+                tiles.append(part + [-1] * (rq - len(part)))
+        tr = torch.tensor(tiles, dtype=torch.int32).cuda()
+        for n_splits in (1, 2):
+            got = torch.zeros(M, H * r, device="cuda")
+            part = torch.zeros(L.latent_tc_partial_floats(len(tiles), n_splits, r), device="cuda")
+            L.latent_attention(q_lat, q, hd, 4, got, M, H, r, rot, 0.2, pos.cuda(), slot.cuda(), table, cache,
+                               tiles=(tr, len(tiles), rq, n_splits, part))
+            live = rows0 + rows1
+            assert torch.allclose(got[live], want[live], atol=2e-2, rtol=2e-2), (H, r, rq, n_splits)
+            assert float(got[27:62:2].abs().max()) == 0.0
 
 
 def test_latent_cache_writer_norms_rotates_and_places_lines():
