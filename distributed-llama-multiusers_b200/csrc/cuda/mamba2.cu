@@ -126,10 +126,103 @@ __global__ void mamba_scan_kernel(DlMambaBatch b, DlMambaScanArgs a) {
         for (int i = 0; i < N; ++i) Sg[i * P + p] = S[i * P + p];
 }
 
+// ------------------------------------------------------------------------------------------------
+// the same scan with the state in registers, for state sizes 16 / 32 / 64 / 128: thread (p, nq) owns rows
+// nq, nq + 4, nq + 8, ... of column p; MS_TB tokens' inputs (B, C, x, step size, decay) are staged per barrier pair,
+// so the token loop touches shared memory and registers only.  y is the sum over the 4 lanes of a column.
+// ------------------------------------------------------------------------------------------------
+#define MS_TB 16
+#define MS_NQ 4
+
+template <int NR>
+__global__ void mamba_scan_reg_kernel(DlMambaBatch b, DlMambaScanArgs a) {
+    extern __shared__ float sm[];
+    const int n = blockIdx.x, h = blockIdx.y;
+    const int N = NR * MS_NQ, P = a.vdim, H = a.n_heads;
+    const int g = h / (H / a.groups);
+    float2* bc = reinterpret_cast<float2*>(sm);          // [MS_TB][N]  (B, C)
+    float* xs = sm + 2 * MS_TB * N;                       // [MS_TB][P]
+    float* ys = xs + MS_TB * P;                           // [MS_TB][P]
+    float* dts = ys + MS_TB * P;                          // [MS_TB]
+    float* dec = dts + MS_TB;                             // [MS_TB]
+    const int tid = threadIdx.x, nq = tid % MS_NQ;
+    const bool act = tid / MS_NQ < P;
+    const int p = act ? tid / MS_NQ : P - 1;              // idle lanes shadow the last column (they take part in the shuffles)
+    float* Sg = a.ssm_state + ((size_t)b.seq_slot[n] * H + h) * N * P;
+    const bool fresh = b.seq_pos0[n] == 0;
+    float s[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) s[i] = fresh ? 0.f : Sg[(size_t)(i * MS_NQ + nq) * P + p];
+    const float A = -expf(a.A_log[h]), Dh = a.D[h], dtb = a.dt_bias[h];
+    const int r0 = b.seq_start[n], r1 = b.seq_start[n + 1];
+    const int inner = H * P, GN = a.groups * N;
+    for (int r = r0; r < r1; r += MS_TB) {
+        const int nt = min(MS_TB, r1 - r);
+        __syncthreads();                                  // the previous block's outputs are stored, its inputs consumed
+        for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+            const int tt = idx / N, i = idx % N;
+            const float* xbc = a.xbc + (size_t)b.seq_rows[r + tt] * a.ld_xbc + inner + g * N + i;
+            bc[idx] = make_float2(xbc[0], xbc[GN]);
+        }
+        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+            const int tt = idx / P, pp = idx % P;
+            xs[idx] = a.xbc[(size_t)b.seq_rows[r + tt] * a.ld_xbc + h * P + pp];
+        }
+        if (tid < nt) {
+            const float dt = softplus_f(a.dt[(size_t)b.seq_rows[r + tid] * a.ld_dt + h] + dtb);
+            dts[tid] = dt;
+            dec[tid] = expf(A * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float x = xs[tt * P + p], dx = dts[tt] * x, d = dec[tt];
+            const float2* row = bc + tt * N + nq;
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                const float2 v = row[i * MS_NQ];
+                s[i] = fmaf(d, s[i], v.x * dx);
+                y = fmaf(s[i], v.y, y);
+            }
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            if (act && nq == 0) ys[tt * P + p] = fmaf(Dh, x, y);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+            const int tt = idx / P, pp = idx % P;
+            a.y[(size_t)b.seq_rows[r + tt] * a.ld_y + h * P + pp] = ys[idx];
+        }
+    }
+    if (act) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) Sg[(size_t)(i * MS_NQ + nq) * P + p] = s[i];
+    }
+}
+
+template <int NR>
+static void launch_scan_reg(const DlMambaBatch& b, const DlMambaScanArgs& a, int n_seq, cudaStream_t st) {
+    const int N = NR * MS_NQ;
+    const size_t smem = ((size_t)2 * MS_TB * N + 2 * (size_t)MS_TB * a.vdim + 2 * MS_TB) * sizeof(float);
+    const int threads = (a.vdim * MS_NQ + 31) / 32 * 32;
+    mamba_scan_reg_kernel<NR><<<dim3(n_seq, a.n_heads), threads, smem, st>>>(b, a);
+}
+
 extern "C" int dl_mamba_scan(const DlMambaBatch* batch, int n_seq, const DlMambaScanArgs* args, void* stream) {
     const DlMambaScanArgs& a = *args;
     if (a.n_heads % a.groups != 0) { dl_set_error("dl_mamba_scan: heads must be a multiple of groups"); return -1; }
     if (a.vdim > 1024) { dl_set_error("dl_mamba_scan: vdim > 1024"); return -1; }
+    if (a.vdim * MS_NQ <= 1024 && a.vdim <= 128 && (a.state == 16 || a.state == 32 || a.state == 64 || a.state == 128)) {
+        cudaStream_t st = (cudaStream_t)stream;
+        switch (a.state) {
+            case 16: launch_scan_reg<4>(*batch, a, n_seq, st); break;
+            case 32: launch_scan_reg<8>(*batch, a, n_seq, st); break;
+            case 64: launch_scan_reg<16>(*batch, a, n_seq, st); break;
+            default: launch_scan_reg<32>(*batch, a, n_seq, st); break;
+        }
+        LAYER_CHECK_LAUNCH("dl_mamba_scan");
+        return 0;
+    }
     const size_t smem = ((size_t)a.state * a.vdim + 2 * (size_t)a.state) * sizeof(float);
     if (smem > 227 * 1024) { dl_set_error("dl_mamba_scan: state %d x vdim %d does not fit shared memory", a.state, a.vdim); return -1; }
     cudaError_t e = cudaFuncSetAttribute(mamba_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -306,10 +306,11 @@ def _run_mixer(eng, h, portions, slot):
     return torch.cat(out)
 
 
-@pytest.mark.parametrize("groups,parts,taps", [(1, 1, 4), (4, 2, 2), (2, 4, 3), (2, 1, 1)])
-def test_mamba2_mixer_alone_whole_and_in_portions(tmp_path, groups, parts, taps):
+@pytest.mark.parametrize("groups,parts,taps,state", [(1, 1, 4, 20), (4, 2, 2, 16), (2, 4, 3, 64), (2, 1, 1, 128), (1, 2, 4, 32)])
+def test_mamba2_mixer_alone_whole_and_in_portions(tmp_path, groups, parts, taps, state):
+    """state 20 runs the scan with the state in shared memory, 16 / 32 / 64 / 128 the one with the state in registers"""
     layer = {"type": "mamba2", "mlp": None,
-             "mixer": {"heads": 4, "vdim": 12, "state": 20, "groups": groups, "conv": taps, "norm_groups": parts}}
+             "mixer": {"heads": 4, "vdim": 12, "state": state, "groups": groups, "conv": taps, "norm_groups": parts}}
     eng, tensors, cfg = _one_layer_engine(tmp_path, layer)
     h = torch.randn(90, 48, generator=torch.Generator().manual_seed(12))
     want = O.mamba2(h.double(), O.sub(tensors, "l0.mix."), layer["mixer"], 1e-5)
