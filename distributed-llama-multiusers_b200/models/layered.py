@@ -105,6 +105,7 @@ class DenseWeight:
 
 
 TC_MIN_ROWS = int(os.environ.get("DLLAMA_LAYERS_TC_MIN_ROWS", "32"))
+GRAPH_MAX_ROWS = 64          # batches up to this many rows are replayed from CUDA graphs
 
 
 # --------------------------------------------------------------------------------------------------
@@ -270,7 +271,8 @@ class _Layer:
 class LayerListEngine:
     def __init__(self, model_path: str, rank: int = 0, world: int = 1, group=None, max_rows: int = 32, n_slots: int = 4,
                  max_seq_len: int = 2048, dtype: str = "bfloat16", n_pages: Optional[int] = None,
-                 device: Optional[torch.device] = None, tensor_cores: Optional[bool] = None, **_unused):
+                 device: Optional[torch.device] = None, tensor_cores: Optional[bool] = None, use_graphs: bool = True,
+                 **_unused):
         if world != 1:
             raise NotImplementedError("layer-list models run on one GPU (no tensor-parallel slicing of their mixers yet)")
         if dtype not in ("bfloat16", "float32"):
@@ -361,6 +363,13 @@ class LayerListEngine:
         self.h_block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32).pin_memory()
         self._staging_ev: Optional[torch.cuda.Event] = None
         self._xh_h_ready = False
+        # decode-sized batches replay a CUDA graph per batch shape (rows, sequences, wanted logits, attention tiling):
+        # a step is ~25 small launches per layer, and the host cannot issue them as fast as the GPU retires them
+        self.use_graphs = bool(use_graphs) and os.environ.get("DLLAMA_LAYERS_GRAPHS", "1") != "0"
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._graph_launches: Dict[tuple, int] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._graph_stream = torch.cuda.Stream(device=dev)
         self.layer_probe = None              # a list: forward() appends a copy of the residual stream after every layer
         torch.cuda.synchronize()
 
@@ -523,6 +532,35 @@ class LayerListEngine:
             else:
                 self.mm(self.head, hn, self.logits, n_logits)
 
+    def _run(self, M: int, n_logits: int, greedy: bool):
+        """Eagerly, or -- for decode-sized batches -- from a CUDA graph.  A shape's first step runs eagerly (it loads
+        modules and sets kernel attributes), its second is captured (capturing executes nothing: the recurrent state
+        advances once per step) and replayed from then on."""
+        from ..ops import lib as _lib
+        key = (M, self.n_seq, n_logits, self._n_tiles, self._n_splits, greedy)
+        if not self.use_graphs or M > GRAPH_MAX_ROWS or self.layer_probe is not None:
+            return self._launch_step(M, n_logits, greedy)
+        g = self._graphs.get(key)
+        if g is None:
+            self._graph_seen[key] = self._graph_seen.get(key, 0) + 1
+            if self._graph_seen[key] < 2:
+                return self._launch_step(M, n_logits, greedy)
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            n0 = _lib.launch_count
+            with torch.cuda.graph(g, stream=self._graph_stream):
+                self._launch_step(M, n_logits, greedy)
+            self._graph_launches[key] = _lib.launch_count - n0
+            _lib.launch_count = n0
+            self._graphs[key] = g
+        g.replay()
+        _lib.count_launch(self._graph_launches[key])
+
+    def _launch_step(self, M: int, n_logits: int, greedy: bool):
+        self._launch_forward(M, n_logits)
+        if greedy and n_logits:
+            self.L.argmax(self.logits, n_logits, self.out_tokens)
+
     @torch.no_grad()
     def forward(self, tokens: Sequence[int], positions: Sequence[int], slots: Sequence[int], logits_from: int = 0,
                 greedy: bool = False, logit_rows: Optional[Sequence[int]] = None) -> torch.Tensor:
@@ -531,9 +569,7 @@ class LayerListEngine:
         `logit_rows`, any rows in any order), valid until the next forward."""
         rows = list(logit_rows) if logit_rows is not None else list(range(logits_from, len(tokens)))
         M = self.set_batch(tokens, positions, slots, rows)
-        self._launch_forward(M, len(rows))
-        if greedy and rows:
-            self.L.argmax(self.logits, len(rows), self.out_tokens)
+        self._run(M, len(rows), greedy)
         return self.logits[:len(rows)]
 
     def prefill(self, slot: int, tokens: Sequence[int], start_pos: int = 0, chunk: Optional[int] = None):
@@ -561,6 +597,7 @@ class LayerListEngine:
         self.L.sample_rows(logits, temperature, topp, coin, tokens_out)
 
     def close(self):
+        self._graphs.clear()
         torch.cuda.synchronize()
 
 
