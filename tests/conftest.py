@@ -21,6 +21,11 @@ def pytest_configure(config):
             _build.build_cuda()
         except Exception as e:          # CPU-only tests do not need it
             print(f"[conftest] CUDA library not built: {e}")
+    if not os.path.exists(os.path.join(lib_dir, "libdllama_b200_layers.so")):
+        try:
+            _build.build_layers()
+        except Exception as e:
+            print(f"[conftest] layer-list CUDA library not built: {e}")
 
 
 def pytest_collection_modifyitems(config, items):
