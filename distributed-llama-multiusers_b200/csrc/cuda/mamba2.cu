@@ -200,6 +200,187 @@ __global__ void mamba_scan_reg_kernel(DlMambaBatch b, DlMambaScanArgs a) {
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Long prompt portions: the recurrence is linear in the state, so a sequence's rows are cut into chunks that run in
+// parallel.  Pass 1 (mamba_chunk_local_kernel): every chunk runs the recurrence from zeros (the sequence's first chunk:
+// from the slot's state), writes its outputs, its final state, its total decay, and per row the decay accumulated since
+// the chunk's start.  Pass 2 (mamba_chunk_fix_kernel): chunk j rebuilds the state it should have started from out of
+// the final states and decays of chunks 0 .. j-1, adds that state's contribution  cum_t * (S_init^T C_t)  to its rows'
+// outputs, and the sequence's last chunk leaves the final state in the slot.
+// ------------------------------------------------------------------------------------------------
+template <int NR>
+__global__ void mamba_chunk_local_kernel(DlMambaBatch b, DlMambaScanArgs a, DlMambaChunks ck) {
+    extern __shared__ float sm[];
+    const int c = blockIdx.x, h = blockIdx.y;
+    const int n = ck.chunk_seq[c], off = ck.chunk_off[c];
+    const int N = NR * MS_NQ, P = a.vdim, H = a.n_heads;
+    const int g = h / (H / a.groups);
+    float2* bc = reinterpret_cast<float2*>(sm);
+    float* xs = sm + 2 * MS_TB * N;
+    float* ys = xs + MS_TB * P;
+    float* dts = ys + MS_TB * P;
+    float* dec = dts + MS_TB;
+    float* cums = dec + MS_TB;                            // [MS_TB + 1]: decay since the chunk's start; [MS_TB] carries over
+    const int tid = threadIdx.x, nq = tid % MS_NQ;
+    const bool act = tid / MS_NQ < P;
+    const int p = act ? tid / MS_NQ : P - 1;
+    const float* Sg = a.ssm_state + ((size_t)b.seq_slot[n] * H + h) * N * P;
+    const bool from_slot = off == 0 && b.seq_pos0[n] != 0;
+    float s[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) s[i] = from_slot ? Sg[(size_t)(i * MS_NQ + nq) * P + p] : 0.f;
+    const float A = -expf(a.A_log[h]), Dh = a.D[h], dtb = a.dt_bias[h];
+    const int r0 = b.seq_start[n] + off, r1 = min(b.seq_start[n + 1], r0 + ck.chunk);
+    const int inner = H * P, GN = a.groups * N;
+    if (tid == 0) cums[MS_TB] = 1.f;
+    for (int r = r0; r < r1; r += MS_TB) {
+        const int nt = min(MS_TB, r1 - r);
+        __syncthreads();
+        for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+            const int tt = idx / N, i = idx % N;
+            const float* xbc = a.xbc + (size_t)b.seq_rows[r + tt] * a.ld_xbc + inner + g * N + i;
+            bc[idx] = make_float2(xbc[0], xbc[GN]);
+        }
+        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+            const int tt = idx / P, pp = idx % P;
+            xs[idx] = a.xbc[(size_t)b.seq_rows[r + tt] * a.ld_xbc + h * P + pp];
+        }
+        if (tid < nt) {
+            const float dt = softplus_f(a.dt[(size_t)b.seq_rows[r + tid] * a.ld_dt + h] + dtb);
+            dts[tid] = dt;
+            dec[tid] = expf(A * dt);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float cv = cums[MS_TB];
+            for (int tt = 0; tt < nt; ++tt) {
+                cv *= dec[tt];
+                cums[tt] = cv;
+                ck.cum[(size_t)b.seq_rows[r + tt] * H + h] = cv;
+            }
+            cums[MS_TB] = cv;
+        }
+        for (int tt = 0; tt < nt; ++tt) {
+            const float x = xs[tt * P + p], dx = dts[tt] * x, d = dec[tt];
+            const float2* row = bc + tt * N + nq;
+            float y = 0.f;
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                const float2 v = row[i * MS_NQ];
+                s[i] = fmaf(d, s[i], v.x * dx);
+                y = fmaf(s[i], v.y, y);
+            }
+            y += __shfl_xor_sync(0xffffffffu, y, 1);
+            y += __shfl_xor_sync(0xffffffffu, y, 2);
+            if (act && nq == 0) ys[tt * P + p] = fmaf(Dh, x, y);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+            const int tt = idx / P, pp = idx % P;
+            a.y[(size_t)b.seq_rows[r + tt] * a.ld_y + h * P + pp] = ys[idx];
+        }
+    }
+    __syncthreads();
+    float* So = ck.state + ((size_t)c * H + h) * N * P;
+    if (act) {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) So[(size_t)(i * MS_NQ + nq) * P + p] = s[i];
+    }
+    if (tid == 0) ck.decay[(size_t)c * H + h] = cums[MS_TB];
+}
+
+template <int NR>
+__global__ void mamba_chunk_fix_kernel(DlMambaBatch b, DlMambaScanArgs a, DlMambaChunks ck) {
+    extern __shared__ float sm[];
+    const int c = blockIdx.x, h = blockIdx.y;
+    const int n = ck.chunk_seq[c], off = ck.chunk_off[c];
+    const int N = NR * MS_NQ, P = a.vdim, H = a.n_heads;
+    const int g = h / (H / a.groups);
+    const int j = off / ck.chunk, c0 = c - j;             // a sequence's chunks are adjacent in the list
+    const int r0 = b.seq_start[n] + off, r1 = min(b.seq_start[n + 1], r0 + ck.chunk);
+    const bool last = r1 == b.seq_start[n + 1];
+    if (j == 0 && !last) return;
+    float* cs = sm;                                       // [MS_TB][N]  C
+    float* ys = cs + MS_TB * N;                           // [MS_TB][P]
+    float* cums = ys + MS_TB * P;                         // [MS_TB]
+    const int tid = threadIdx.x, nq = tid % MS_NQ;
+    const bool act = tid / MS_NQ < P;
+    const int p = act ? tid / MS_NQ : P - 1;
+    float s[NR];
+#pragma unroll
+    for (int i = 0; i < NR; ++i) s[i] = 0.f;
+    for (int jj = 0; jj < j; ++jj) {
+        const float d = ck.decay[(size_t)(c0 + jj) * H + h];
+        const float* Sj = ck.state + ((size_t)(c0 + jj) * H + h) * N * P;
+#pragma unroll
+        for (int i = 0; i < NR; ++i) s[i] = fmaf(d, s[i], Sj[(size_t)(i * MS_NQ + nq) * P + p]);
+    }
+    if (j > 0) {
+        const int inner = H * P, GN = a.groups * N;
+        for (int r = r0; r < r1; r += MS_TB) {
+            const int nt = min(MS_TB, r1 - r);
+            __syncthreads();
+            for (int idx = tid; idx < nt * N; idx += blockDim.x) {
+                const int tt = idx / N, i = idx % N;
+                cs[idx] = a.xbc[(size_t)b.seq_rows[r + tt] * a.ld_xbc + inner + GN + g * N + i];
+            }
+            if (tid < nt) cums[tid] = ck.cum[(size_t)b.seq_rows[r + tid] * H + h];
+            __syncthreads();
+            for (int tt = 0; tt < nt; ++tt) {
+                const float* row = cs + tt * N + nq;
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < NR; ++i) y = fmaf(s[i], row[i * MS_NQ], y);
+                y += __shfl_xor_sync(0xffffffffu, y, 1);
+                y += __shfl_xor_sync(0xffffffffu, y, 2);
+                if (act && nq == 0) ys[tt * P + p] = cums[tt] * y;
+            }
+            __syncthreads();
+            for (int idx = tid; idx < nt * P; idx += blockDim.x) {
+                const int tt = idx / P, pp = idx % P;
+                a.y[(size_t)b.seq_rows[r + tt] * a.ld_y + h * P + pp] += ys[idx];
+            }
+        }
+    }
+    if (last && act) {
+        const float d = ck.decay[(size_t)c * H + h];
+        const float* Sc = ck.state + ((size_t)c * H + h) * N * P;
+        float* Sg = a.ssm_state + ((size_t)b.seq_slot[n] * H + h) * N * P;
+#pragma unroll
+        for (int i = 0; i < NR; ++i) Sg[(size_t)(i * MS_NQ + nq) * P + p] = fmaf(d, s[i], Sc[(size_t)(i * MS_NQ + nq) * P + p]);
+    }
+}
+
+template <int NR>
+static void launch_scan_chunked(const DlMambaBatch& b, const DlMambaScanArgs& a, const DlMambaChunks& ck, cudaStream_t st) {
+    const int N = NR * MS_NQ;
+    const size_t smem = ((size_t)2 * MS_TB * N + 2 * (size_t)MS_TB * a.vdim + 3 * MS_TB + 1) * sizeof(float);
+    const int threads = (a.vdim * MS_NQ + 31) / 32 * 32;
+    mamba_chunk_local_kernel<NR><<<dim3(ck.n_chunks, a.n_heads), threads, smem, st>>>(b, a, ck);
+    mamba_chunk_fix_kernel<NR><<<dim3(ck.n_chunks, a.n_heads), threads, smem, st>>>(b, a, ck);
+}
+
+extern "C" int dl_mamba_scan_chunked_supported(int vdim, int state) {
+    return (vdim * MS_NQ <= 1024 && vdim <= 128 && (state == 16 || state == 32 || state == 64 || state == 128)) ? 0 : -1;
+}
+
+// scratch: ck.state [n_chunks][heads][state][vdim], ck.decay [n_chunks][heads], ck.cum [rows][heads] (all f32)
+extern "C" int dl_mamba_scan_chunked(const DlMambaBatch* batch, const DlMambaScanArgs* args, const DlMambaChunks* chunks, void* stream) {
+    const DlMambaScanArgs& a = *args;
+    if (a.n_heads % a.groups != 0) { dl_set_error("dl_mamba_scan_chunked: heads must be a multiple of groups"); return -1; }
+    if (dl_mamba_scan_chunked_supported(a.vdim, a.state) != 0) { dl_set_error("dl_mamba_scan_chunked: vdim %d / state %d not supported", a.vdim, a.state); return -1; }
+    if (chunks->n_chunks < 1 || chunks->chunk < MS_TB) { dl_set_error("dl_mamba_scan_chunked: bad chunking"); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (a.state) {
+        case 16: launch_scan_chunked<4>(*batch, a, *chunks, st); break;
+        case 32: launch_scan_chunked<8>(*batch, a, *chunks, st); break;
+        case 64: launch_scan_chunked<16>(*batch, a, *chunks, st); break;
+        default: launch_scan_chunked<32>(*batch, a, *chunks, st); break;
+    }
+    LAYER_CHECK_LAUNCH("dl_mamba_scan_chunked");
+    return 0;
+}
+
 template <int NR>
 static void launch_scan_reg(const DlMambaBatch& b, const DlMambaScanArgs& a, int n_seq, cudaStream_t st) {
     const int N = NR * MS_NQ;

@@ -105,6 +105,7 @@ class DenseWeight:
 
 
 TC_MIN_ROWS = int(os.environ.get("DLLAMA_LAYERS_TC_MIN_ROWS", "32"))
+CHUNKED_SCAN_MIN_ROWS = 256  # a batch holding this many rows of one sequence runs the recurrence chunk-parallel
 GRAPH_MAX_ROWS = 64          # batches up to this many rows are replayed from CUDA graphs
 
 
@@ -219,7 +220,7 @@ class Mamba2Mixer:
         L.mamba_conv(e.mamba_batch, M, e.n_seq, zx, self.inner, self.w_conv, self.b_conv, self.conv_state, xbc)
         dt = zx[:, 2 * self.inner + 2 * self.G * self.N:]
         L.mamba_scan(e.mamba_batch, e.n_seq, xbc, dt, self.dt_bias, self.A_log, self.D, ys, self.ssm_state, self.H, self.P,
-                     self.N, self.G)
+                     self.N, self.G, chunks=e.mamba_chunks(self))
         L.rms_norm(ys, yn, M, self.inner, e.cfg.norm_eps, w=self.norm, groups=self.norm_groups, gate=zx)
         e.mm(self.w_o, yn, y, M)
 
@@ -324,6 +325,15 @@ class LayerListEngine:
         if self.attn_rq:
             rmax = max(mx.rank for mx in att)
             self._attn_partial = torch.zeros(L.latent_tc_partial_floats(3 * self.n_sms, 1, rmax), dtype=torch.float32, device=dev)
+        # long prompt portions run the recurrence in chunks of L.MAMBA_CHUNK rows in parallel (two passes)
+        mam = [mx for mx in mixers if isinstance(mx, Mamba2Mixer) and L.mamba_chunked_supported(mx.P, mx.N)]
+        self._n_chunks, self._chunk_scratch = 0, None
+        self._max_chunks = R // L.MAMBA_CHUNK + self.n_slots
+        if mam and R >= CHUNKED_SCAN_MIN_ROWS and os.environ.get("DLLAMA_LAYERS_CHUNKED_SCAN", "1") != "0":
+            self._chunk_scratch = (
+                torch.zeros(self._max_chunks * max(mx.H * mx.N * mx.P for mx in mam), dtype=torch.float32, device=dev),
+                torch.zeros(self._max_chunks * max(mx.H for mx in mam), dtype=torch.float32, device=dev),
+                torch.zeros(R * max(mx.H for mx in mam), dtype=torch.float32, device=dev))
         # scratch: one f32 buffer per name, as wide as the widest user
         widths: Dict[str, int] = {}
         for l in self.layers:
@@ -348,7 +358,8 @@ class LayerListEngine:
         #   tokens | pos | slot | row_seq | seq_rows | logit_rows   [R] each, then seq_start [S+1] | seq_slot [S] | seq_pos0 [S]
         S = self.n_slots
         self._tiles_off = 6 * R + 3 * S + 1                  # then tile_rows [n_tiles][rq] of the attention kernel
-        self._desc_len = self._tiles_off + R + 16 * S
+        self._chunks_off = self._tiles_off + R + 16 * S      # then chunk_seq | chunk_off [max_chunks] of the chunked scan
+        self._desc_len = self._chunks_off + 2 * self._max_chunks
         self.tile_rows = None
         self.h_desc = torch.zeros(self._desc_len, dtype=torch.int32).pin_memory()
         self.desc = torch.zeros(self._desc_len, dtype=torch.int32, device=dev)
@@ -356,7 +367,9 @@ class LayerListEngine:
         self.tokens, self.pos, self.slot, self.row_seq, self.seq_rows, self.logit_rows = (d[i * R:(i + 1) * R] for i in range(6))
         o = 6 * R
         self.seq_start, self.seq_slot, self.seq_pos0 = d[o:o + S + 1], d[o + S + 1:o + 2 * S + 1], d[o + 2 * S + 1:o + 3 * S + 1]
-        self.tile_rows = d[self._tiles_off:]
+        self.tile_rows = d[self._tiles_off:self._chunks_off]
+        self.chunk_seq = d[self._chunks_off:self._chunks_off + self._max_chunks]
+        self.chunk_off = d[self._chunks_off + self._max_chunks:]
         self.mamba_batch = L.mamba_batch(self.pos, self.row_seq, self.seq_start, self.seq_rows, self.seq_slot, self.seq_pos0)
         self.n_seq = 0
         self.block_table = torch.zeros(self.n_slots, self.max_pages, dtype=torch.int32, device=dev)
@@ -413,6 +426,13 @@ class LayerListEngine:
         for h in range(w.t.shape[0]):
             L.xh_from_rows(x[:, h * x_head_stride:], M, w.K, self.ncap, self._xh["tmp"])
             L.dense_tc(w.wh[h], w.N, w.K, self._xh["tmp"], self.ncap, y[:, h * y_head_stride:], M)
+
+    def mamba_chunks(self, mx):
+        """The chunking of this batch for the two-pass scan, or None where the token-by-token scan runs (short portions,
+        decoding, sizes the chunked kernels do not take)."""
+        if not self._n_chunks or not self.L.mamba_chunked_supported(mx.P, mx.N):
+            return None
+        return (self.chunk_seq, self.chunk_off, self._n_chunks) + self._chunk_scratch
 
     def latent_tiles(self, mx):
         """The row tiling of this batch for the tensor-core attention kernel, or None where the per-row kernel runs."""
@@ -495,6 +515,14 @@ class LayerListEngine:
                 pages = max(pages, (int(self._slot_len[s]) + PAGE - 1) // PAGE)
             self._n_tiles = nt
             self._n_splits = 1 if nt >= self.n_sms else max(1, min(32, (2 * self.n_sms) // nt, pages // 2))
+        self._n_chunks = 0
+        if self._chunk_scratch is not None and max(len(r) for r in by_slot.values()) >= CHUNKED_SCAN_MIN_ROWS:
+            co, nc, ch = self._chunks_off, 0, self.L.MAMBA_CHUNK
+            for n, rows in enumerate(by_slot.values()):
+                for off in range(0, len(rows), ch):
+                    hd[co + nc], hd[co + self._max_chunks + nc] = n, off
+                    nc += 1
+            self._n_chunks = nc
         nl = len(logit_rows)
         hd[5 * R:5 * R + nl] = logit_rows
         if self.pages.dirty:

@@ -11,7 +11,7 @@ import torch
 
 from . import lib
 from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
-                  DlEpilogue, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
+                  DlEpilogue, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
 
@@ -195,14 +195,29 @@ def mamba_conv(batch: DlMambaBatch, M: int, n_seq: int, zx: torch.Tensor, in_off
     lib.count_launch(2 if taps > 1 else 1)
 
 
+MAMBA_CHUNK = 128            # rows of a sequence per chunk of the chunked scan
+
+
+def mamba_chunked_supported(vdim: int, state: int) -> bool:
+    return layers_lib().dl_mamba_scan_chunked_supported(vdim, state) == 0
+
+
 def mamba_scan(batch: DlMambaBatch, n_seq: int, xbc: torch.Tensor, dt: torch.Tensor, dt_bias, A_log, D, y: torch.Tensor,
-               ssm_state: torch.Tensor, n_heads: int, vdim: int, state: int, groups: int):
-    """dt: a view whose element [m, h] is the raw step size of head h of row m."""
+               ssm_state: torch.Tensor, n_heads: int, vdim: int, state: int, groups: int, chunks=None):
+    """dt: a view whose element [m, h] is the raw step size of head h of row m.  chunks = (chunk_seq, chunk_off, n_chunks,
+    state scratch, decay scratch, cum scratch): the two-pass scan over chunks of MAMBA_CHUNK rows run in parallel."""
     a = DlMambaScanArgs()
     a.xbc, a.ld_xbc, a.dt, a.ld_dt = xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0)
     a.dt_bias, a.A_log, a.D = dt_bias.data_ptr(), A_log.data_ptr(), D.data_ptr()
     a.y, a.ld_y, a.ssm_state = y.data_ptr(), y.stride(0), ssm_state.data_ptr()
     a.n_heads, a.vdim, a.state, a.groups = n_heads, vdim, state, groups
+    if chunks is not None:
+        c = DlMambaChunks()
+        c.chunk_seq, c.chunk_off, c.n_chunks, c.chunk = chunks[0].data_ptr(), chunks[1].data_ptr(), chunks[2], MAMBA_CHUNK
+        c.state, c.decay, c.cum = chunks[3].data_ptr(), chunks[4].data_ptr(), chunks[5].data_ptr()
+        check_layers(layers_lib().dl_mamba_scan_chunked(batch, a, c, _stream()), "dl_mamba_scan_chunked")
+        lib.count_launch(2)
+        return
     check_layers(layers_lib().dl_mamba_scan(batch, n_seq, a, _stream()), "dl_mamba_scan")
     lib.count_launch()
 

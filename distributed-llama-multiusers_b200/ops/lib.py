@@ -271,6 +271,12 @@ class DlMambaScanArgs(C.Structure):
                 ("n_heads", C.c_int), ("vdim", C.c_int), ("state", C.c_int), ("groups", C.c_int)]
 
 
+class DlMambaChunks(C.Structure):
+    """Mirror of ``DlMambaChunks``."""
+    _fields_ = [("chunk_seq", C.c_void_p), ("chunk_off", C.c_void_p), ("n_chunks", C.c_int), ("chunk", C.c_int),
+                ("state", C.c_void_p), ("decay", C.c_void_p), ("cum", C.c_void_p)]
+
+
 _layers = None
 
 
@@ -299,6 +305,9 @@ def layers_lib():
     L.dl_latent_tc_partial_floats.restype = i64
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
+    L.dl_mamba_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), C.POINTER(DlMambaScanArgs), C.POINTER(DlMambaChunks), vp]
+    L.dl_mamba_scan_chunked_supported.argtypes = [i32, i32]
+    L.dl_mamba_scan_chunked_supported.restype = i32
     L.dl_wh_bytes.restype = i64
     L.dl_wh_bytes.argtypes = [i32, i32]
     L.dl_wh_from_dense.argtypes = [vp, i32, i32, i64, vp, vp]
@@ -309,7 +318,7 @@ def layers_lib():
     L.dl_argmax_scratch_bytes.restype = i64
     L.dl_argmax_scratch_bytes.argtypes = [i32]
     for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention", "dl_latent_attention_tc",
-                 "dl_mamba_conv", "dl_mamba_scan", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
+                 "dl_mamba_conv", "dl_mamba_scan", "dl_mamba_scan_chunked", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
                  "dl_gemm_wh_tc"):
         getattr(L, name).restype = i32
     _layers = L

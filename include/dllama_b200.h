@@ -410,6 +410,17 @@ typedef struct {
     int n_heads, vdim, state, groups;
 } DlMambaScanArgs;
 int dl_mamba_scan(const DlMambaBatch* batch /*host*/, int n_seq, const DlMambaScanArgs* args /*host*/, void* stream);
+/* The same scan for long prompt portions, chunks of `chunk` rows of a sequence in parallel (two launches).  chunk_seq /
+ * chunk_off [n_chunks] (device): the sequence and the offset among its rows of every chunk, a sequence's chunks adjacent
+ * and in order.  Scratch (f32): state [n_chunks][heads][state][vdim], decay [n_chunks][heads], cum [rows][heads]. */
+typedef struct {
+    const int* chunk_seq; const int* chunk_off;
+    int n_chunks, chunk;
+    float* state; float* decay; float* cum;
+} DlMambaChunks;
+int dl_mamba_scan_chunked_supported(int vdim, int state);
+int dl_mamba_scan_chunked(const DlMambaBatch* batch /*host*/, const DlMambaScanArgs* args /*host*/,
+                          const DlMambaChunks* chunks /*host*/, void* stream);
 
 #ifdef __cplusplus
 }

@@ -324,6 +324,49 @@ def test_mamba2_mixer_alone_whole_and_in_portions(tmp_path, groups, parts, taps,
     assert torch.allclose(got.double().cpu(), want, atol=3e-4, rtol=1e-3)
 
 
+@pytest.mark.parametrize("state,groups", [(16, 1), (64, 2), (128, 4)])
+def test_mamba2_chunk_parallel_scan(tmp_path, state, groups):
+    """Portions of 256 rows and more run the recurrence in chunks of 128 rows in parallel (two passes): a long portion
+    from position 0, one that continues a state, two sequences of unequal length in one batch, chunk tails of 1 row."""
+    from dllama_b200.models.layered import write_random_model
+    layer = {"type": "mamba2", "mlp": None,
+             "mixer": {"heads": 4, "vdim": 12, "state": state, "groups": groups, "conv": 4, "norm_groups": 2}}
+    cfg = {"architecture": "Ribivik", "width": 48, "vocab": 64, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": [layer]}
+    tensors = write_random_model(str(tmp_path), cfg, seed=17)
+    eng = _engine(str(tmp_path), max_rows=700, n_slots=3, seq=1024)
+    assert eng._chunk_scratch is not None
+    h = torch.randn(641, 48, generator=torch.Generator().manual_seed(18))
+    want = O.mamba2(h.double(), O.sub(tensors, "l0.mix."), layer["mixer"], 1e-5)
+    s0 = eng.alloc_slot()
+    got = _run_mixer(eng, h.cuda(), [641], s0)                                   # 5 chunks of 128 + a chunk of 1
+    assert eng._n_chunks == 6
+    assert torch.allclose(got.double().cpu(), want, atol=3e-4, rtol=1e-3)
+    s1 = eng.alloc_slot()
+    got = _run_mixer(eng, h.cuda(), [3, 300, 1, 337], s1)                        # token-by-token kernel, chunked, again, chunked
+    assert torch.allclose(got.double().cpu(), want, atol=3e-4, rtol=1e-3)
+    # two sequences in one batch, rows interleaved; slot s0 starts again at 0, a third slot continues later
+    s2 = eng.alloc_slot()
+    _run_mixer(eng, h.cuda(), [50], s2)
+    rows_a, rows_b = list(range(0, 600, 2)), list(range(1, 601, 2))[:291]
+    M = 600
+    toks, pos, slots = [0] * M, [0] * M, [0] * M
+    hin = torch.zeros(M, 48)
+    for i, m in enumerate(rows_a):
+        pos[m], slots[m], hin[m] = i, s0, h[i]
+    for i, m in enumerate(rows_b):
+        pos[m], slots[m], hin[m] = 50 + i, s2, h[50 + i]
+    fill = sorted(set(range(M)) - set(rows_a) - set(rows_b))                      # the rest: a third sequence
+    for i, m in enumerate(fill):
+        pos[m], slots[m], hin[m] = 641 + i, s1, h[i]
+    eng.set_batch(toks, pos, slots, [])
+    eng.hn[:M] = hin.cuda()
+    eng.begin_sublayer()
+    eng.layers[0].mixer.forward(eng.hn, eng.y, M)
+    y = eng.y[:M].double().cpu()
+    assert torch.allclose(y[rows_a], want[:300], atol=3e-4, rtol=1e-3)
+    assert torch.allclose(y[rows_b], want[50:341], atol=3e-4, rtol=1e-3)
+
+
 def test_latent_attention_mixer_alone_whole_and_in_portions(tmp_path):
     layer = {"type": "latent_attention", "mlp": None,
              "mixer": {"heads": 3, "dim": 10, "rot_dim": 6, "vdim": 14, "q_rank": 18, "kv_rank": 22, "scale": 0.3,
