@@ -171,7 +171,7 @@ extern "C" int dl_latent_attention(const DlLatentAttnArgs* args, int M, void* st
 }
 
 // ------------------------------------------------------------------------------------------------
-// Tensor-core variant (bf16 cache): a CTA owns a tile of up to LQ_ROWS "query rows x heads" of one sequence
+// Tensor-core variant (bf16 cache): a CTA owns a tile of up to 16 * NI (32 or 64) "query rows x heads" of one sequence
 // (consecutive positions x all heads: every head reads the same cache lines, so heads stack on the M dimension of
 // the MMA) and walks the sequence's pages.  Per page (32 tokens):
 //     S[32 x 32]  = Q[32 x D] . C[32 x D]^T        each of the NJ column-warps takes D / NJ of the K dimension;
@@ -179,18 +179,26 @@ extern "C" int dl_latent_attention(const DlLatentAttnArgs* args, int M, void* st
 //     softmax     (f32, online; every warp of a row tile redoes the cheap 16 x 32 part)
 //     O[32 x R]  += P[32 x 32] . C[32 x R]         each column-warp owns R / NJ output columns in registers
 // Warps: NI row tiles of 16 x NJ column-warps.  mma.sync m16n8k16 bf16; B fragments of P.C by ldmatrix.trans.
+// Pages arrive by cp.async into two buffers: page k + 1 is in flight while page k is multiplied.
 // With `n_splits` > 1 (decode: few tiles, long contexts) CTAs along grid.y take page ranges and leave unnormalised
 // partial sums that latent_merge_kernel combines.
 // ------------------------------------------------------------------------------------------------
-#define LQ_ROWS 32
+#define LQ_MAX_ROWS 64
 #define LQ_NJ 4
-#define LQ_NI (LQ_ROWS / 16)
-#define LQ_THREADS (32 * LQ_NJ * LQ_NI)
-#define LQ_SP_LD 33
+#define LQ_SP_LD 34                       // even: partial scores move as float2
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem_row) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
 }
 __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -198,18 +206,19 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// NT: n-tiles (8 columns) of O per column-warp; the kernel covers rank <= NT * 8 * LQ_NJ
-template <int NT>
-__global__ void __launch_bounds__(LQ_THREADS) latent_attention_mma_kernel(DlLatentAttnArgs a, DlLatentTiles tl) {
+// NT: n-tiles (8 columns) of O per column-warp; the kernel covers rank <= NT * 8 * LQ_NJ.  NI: row tiles of 16.
+template <int NT, int NI>
+__global__ void __launch_bounds__(32 * LQ_NJ * NI) latent_attention_mma_kernel(DlLatentAttnArgs a, DlLatentTiles tl) {
+    constexpr int LQ_ROWS = 16 * NI, LQ_THREADS = 32 * LQ_NJ * NI;
     extern __shared__ __align__(16) uint8_t smraw[];
     const int H = a.n_heads, R = a.rank, D = a.rank + a.rot;
     const int Dp = tl.d_pad, LD = Dp + 8;                 // row stride in bf16: 16-byte multiple, conflict-free
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smraw);         // [LQ_ROWS][LD]
-    __nv_bfloat16* c_s = q_s + LQ_ROWS * LD;                              // [32][LD]
-    float* sp = reinterpret_cast<float*>(c_s + 32 * LD);                  // [LQ_NI][LQ_NJ][16][LQ_SP_LD]
+    __nv_bfloat16* c_buf = q_s + LQ_ROWS * LD;                            // [2][32][LD]
+    float* sp = reinterpret_cast<float*>(c_buf + 2 * 32 * LD);            // [NI][LQ_NJ][16][LQ_SP_LD]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wi = warp / LQ_NJ, wj = warp % LQ_NJ, g = lane >> 2, t = lane & 3;
-    const int tile = blockIdx.x, split = blockIdx.y;
+    const int tile = tl.n_tiles - 1 - blockIdx.x, split = blockIdx.y;   // a sequence's later tiles walk more pages: start them first
     const int* trows = tl.tile_rows + (size_t)tile * tl.rq;
     const int row_first = trows[0];
     const int slot = a.slot[row_first], pos0 = a.pos[row_first];
@@ -240,64 +249,72 @@ __global__ void __launch_bounds__(LQ_THREADS) latent_attention_mma_kernel(DlLate
     const int p_begin = split * per, p_end = min(n_pages, p_begin + per);
     const int ks_per = Dp / LQ_NJ / 16;                  // k steps of this warp's share of D
     const int ocol0 = wj * NT * 8;                       // this warp's output columns
-    for (int pg = p_begin; pg < p_end; ++pg) {
-        __syncthreads();                                  // q_s staged; previous page's tile and partial scores consumed
+    // page `pg` -> buffer `buf`: lines past the last position and the padding columns are zeroed, the rest is copied
+    // asynchronously (16-byte chunks)
+    auto stage = [&](int pg, int buf) {
         const int page = a.block_table[(size_t)slot * a.max_pages + pg];
         const __nv_bfloat16* src = (const __nv_bfloat16*)a.cache + (size_t)page * 32 * D;
+        __nv_bfloat16* dst = c_buf + buf * 32 * LD;
         const int valid = min(32, last_pos + 1 - pg * 32);
         const int dv = D >> 3, dpv = Dp >> 3;             // 16-byte chunks per line
         for (int i = tid; i < 32 * dpv; i += LQ_THREADS) {
             const int j = i / dpv, c = i % dpv;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (j < valid && c < dv) v = *reinterpret_cast<const uint4*>(src + (size_t)j * D + c * 8);
-            *reinterpret_cast<uint4*>(c_s + j * LD + c * 8) = v;
+            if (j < valid && c < dv) cp_async16(dst + j * LD + c * 8, src + (size_t)j * D + c * 8);
+            else *reinterpret_cast<uint4*>(dst + j * LD + c * 8) = make_uint4(0u, 0u, 0u, 0u);
         }
-        __syncthreads();
+    };
+    if (p_begin < p_end) stage(p_begin, 0);
+    for (int pg = p_begin; pg < p_end; ++pg) {
+        const int cur = (pg - p_begin) & 1;
+        const __nv_bfloat16* c_s = c_buf + cur * 32 * LD;
+        cp_async_wait_all();
+        __syncthreads();                                  // this page has landed (and q_s is staged); everybody is done with the other buffer
+        if (pg + 1 < p_end) stage(pg + 1, cur ^ 1);
         // ---- partial scores over this warp's share of D ----
         float s[4][4];
 #pragma unroll
         for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
         for (int ks = 0; ks < ks_per; ++ks) {
             const int k0 = (wj * ks_per + ks) * 16;
+            const int mat = lane >> 3, rr = lane & 7;     // each lane addresses one row of one 8 x 8 block
             uint32_t af[4];
-            const __nv_bfloat16* qa = q_s + (wi * 16 + g) * LD + k0 + 2 * t;
-            af[0] = *reinterpret_cast<const uint32_t*>(qa);
-            af[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD);
-            af[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
-            af[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * LD + 8);
+            ldmatrix_x4(af, q_s + (wi * 16 + (mat & 1) * 8 + rr) * LD + k0 + (mat >> 1) * 8);
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const __nv_bfloat16* cb = c_s + (n * 8 + g) * LD + k0 + 2 * t;
-                mma_bf16(s[n], af, *reinterpret_cast<const uint32_t*>(cb), *reinterpret_cast<const uint32_t*>(cb + 8));
+            for (int n = 0; n < 4; n += 2) {
+                uint32_t bf[4];                           // tokens of n-tiles n, n + 1 x the two k halves
+                ldmatrix_x4(bf, c_s + ((n + (mat >> 1)) * 8 + rr) * LD + k0 + (mat & 1) * 8);
+                mma_bf16(s[n], af, bf[0], bf[1]);
+                mma_bf16(s[n + 1], af, bf[2], bf[3]);
             }
         }
         float* my_sp = sp + ((wi * LQ_NJ + wj) * 16) * LQ_SP_LD;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
-            my_sp[g * LQ_SP_LD + n * 8 + 2 * t] = s[n][0];
-            my_sp[g * LQ_SP_LD + n * 8 + 2 * t + 1] = s[n][1];
-            my_sp[(g + 8) * LQ_SP_LD + n * 8 + 2 * t] = s[n][2];
-            my_sp[(g + 8) * LQ_SP_LD + n * 8 + 2 * t + 1] = s[n][3];
+            *reinterpret_cast<float2*>(my_sp + g * LQ_SP_LD + n * 8 + 2 * t) = make_float2(s[n][0], s[n][1]);
+            *reinterpret_cast<float2*>(my_sp + (g + 8) * LQ_SP_LD + n * 8 + 2 * t) = make_float2(s[n][2], s[n][3]);
         }
         __syncthreads();
         // ---- softmax of rows g, g + 8; this lane's tokens: 2t, 2t+1, 2t+8, 2t+9, 2t+16, ... (the A fragment of P.C) ----
         float p0[8], p1[8];
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int col = (e >> 1) * 8 + 2 * t + (e & 1);
-            float v0 = 0.f, v1 = 0.f;
+        for (int e2 = 0; e2 < 4; ++e2) {
+            const int col = e2 * 8 + 2 * t;
+            float2 v0 = make_float2(0.f, 0.f), v1 = make_float2(0.f, 0.f);
 #pragma unroll
             for (int j = 0; j < LQ_NJ; ++j) {
                 const float* q = sp + ((wi * LQ_NJ + j) * 16) * LQ_SP_LD;
-                v0 += q[g * LQ_SP_LD + col];
-                v1 += q[(g + 8) * LQ_SP_LD + col];
+                const float2 u0 = *reinterpret_cast<const float2*>(q + g * LQ_SP_LD + col);
+                const float2 u1 = *reinterpret_cast<const float2*>(q + (g + 8) * LQ_SP_LD + col);
+                v0.x += u0.x; v0.y += u0.y; v1.x += u1.x; v1.y += u1.y;
             }
             const int tok = pg * 32 + col;
-            p0[e] = (live0 && tok <= qpos0) ? v0 * a.scale : -INFINITY;
-            p1[e] = (live1 && tok <= qpos1) ? v1 * a.scale : -INFINITY;
-            mx0 = fmaxf(mx0, p0[e]);
-            mx1 = fmaxf(mx1, p1[e]);
+            p0[2 * e2] = (live0 && tok <= qpos0) ? v0.x * a.scale : -INFINITY;
+            p0[2 * e2 + 1] = (live0 && tok + 1 <= qpos0) ? v0.y * a.scale : -INFINITY;
+            p1[2 * e2] = (live1 && tok <= qpos1) ? v1.x * a.scale : -INFINITY;
+            p1[2 * e2 + 1] = (live1 && tok + 1 <= qpos1) ? v1.y * a.scale : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(p0[2 * e2], p0[2 * e2 + 1]));
+            mx1 = fmaxf(mx1, fmaxf(p1[2 * e2], p1[2 * e2 + 1]));
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
@@ -359,7 +376,7 @@ __global__ void __launch_bounds__(LQ_THREADS) latent_attention_mma_kernel(DlLate
     } else {
         // partial[tile][split][mr][rpad + 2]: unnormalised sums, then running maximum and row sum
         const int rpad = NT * 8 * LQ_NJ;
-        float* base = tl.partial + (((size_t)tile * tl.n_splits + split) * LQ_ROWS) * (rpad + 2);
+        float* base = tl.partial + (((size_t)tile * tl.n_splits + split) * LQ_MAX_ROWS) * (rpad + 2);
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int mr = half ? mr1 : mr0;
@@ -382,8 +399,8 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(DlLatentAttnArgs a, D
     if (mr / H >= tl.rq) return;
     const int row = trows[mr / H], h = mr % H;
     if (row < 0) return;
-    const float* base = tl.partial + ((size_t)tile * tl.n_splits * LQ_ROWS + mr) * (rpad + 2);
-    const size_t sstride = (size_t)LQ_ROWS * (rpad + 2);
+    const float* base = tl.partial + ((size_t)tile * tl.n_splits * LQ_MAX_ROWS + mr) * (rpad + 2);
+    const size_t sstride = (size_t)LQ_MAX_ROWS * (rpad + 2);
     float mx = -INFINITY;
     for (int s = 0; s < tl.n_splits; ++s) mx = fmaxf(mx, base[s * sstride + rpad]);
     float den = 0.f;
@@ -409,22 +426,34 @@ extern "C" int dl_latent_tc_rpad(int rank) {
 }
 extern "C" long long dl_latent_tc_partial_floats(int n_tiles, int n_splits, int rank) {
     const int rpad = dl_latent_tc_rpad(rank);
-    return rpad < 0 ? -1 : (long long)n_tiles * n_splits * LQ_ROWS * (rpad + 2);
+    return rpad < 0 ? -1 : (long long)n_tiles * n_splits * LQ_MAX_ROWS * (rpad + 2);
 }
 
-// 0 if these sizes run on the tensor-core kernel (bf16 cache, heads stacked into 32 rows, 16-byte cache lines)
+// 0 if these sizes run on the tensor-core kernel (bf16 cache, rows x heads stacked into <= 64 rows, 16-byte cache lines)
 extern "C" int dl_latent_attention_tc_supported(int n_heads, int rank, int rot, int ctype, int rq) {
-    if (ctype != DL_T_BF16 || n_heads < 1 || rq < 1 || rq * n_heads > LQ_ROWS) return -1;
+    if (ctype != DL_T_BF16 || n_heads < 1 || rq < 1 || rq * n_heads > LQ_MAX_ROWS) return -1;
     if ((rank + rot) % 8 != 0 || dl_latent_tc_rpad(rank) < 0) return -1;
     return 0;
 }
 
-template <int NT>
-static int launch_latent_mma(const DlLatentAttnArgs& a, const DlLatentTiles& tl, size_t smem, cudaStream_t st) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static size_t latent_mma_smem(int ni, int dp) {
+    return (size_t)(16 * ni + 2 * 32) * (dp + 8) * 2 + (size_t)ni * LQ_NJ * 16 * LQ_SP_LD * 4;
+}
+
+template <int NT, int NI>
+static int launch_latent_mma_ni(const DlLatentAttnArgs& a, const DlLatentTiles& tl, cudaStream_t st) {
+    const size_t smem = latent_mma_smem(NI, tl.d_pad);
+    if (smem > 227 * 1024) { dl_set_error("dl_latent_attention_tc: rank %d needs %zu bytes of shared memory", a.rank, smem); return -1; }
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<NT, NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { dl_set_error("dl_latent_attention_tc: shared memory attribute: %s", cudaGetErrorString(e)); return -(int)e; }
-    latent_attention_mma_kernel<NT><<<dim3(tl.n_tiles, tl.n_splits), LQ_THREADS, smem, st>>>(a, tl);
+    latent_attention_mma_kernel<NT, NI><<<dim3(tl.n_tiles, tl.n_splits), 32 * LQ_NJ * NI, smem, st>>>(a, tl);
     return 0;
+}
+
+// tiles of up to 32 stacked rows run with 8 warps, larger ones (up to 64) with 16
+template <int NT>
+static int launch_latent_mma(const DlLatentAttnArgs& a, const DlLatentTiles& tl, cudaStream_t st) {
+    return tl.rq * a.n_heads > 32 ? launch_latent_mma_ni<NT, 4>(a, tl, st) : launch_latent_mma_ni<NT, 2>(a, tl, st);
 }
 
 extern "C" int dl_latent_attention_tc(const DlLatentAttnArgs* args, const DlLatentTiles* tiles, void* stream) {
@@ -441,15 +470,13 @@ extern "C" int dl_latent_attention_tc(const DlLatentAttnArgs* args, const DlLate
     int dp = (a.rank + a.rot + unit - 1) / unit * unit;
     if (dp < rpad) dp = rpad;                             // P.C reads `rpad` columns of every staged line
     tl.d_pad = dp;
-    const size_t smem = (size_t)(LQ_ROWS + 32) * (dp + 8) * 2 + (size_t)LQ_NI * LQ_NJ * 16 * LQ_SP_LD * 4;
-    if (smem > 227 * 1024) { dl_set_error("dl_latent_attention_tc: rank %d needs %zu bytes of shared memory", a.rank, smem); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
     switch (rpad / (8 * LQ_NJ)) {
-        case 2: rc = launch_latent_mma<2>(a, tl, smem, st); break;
-        case 4: rc = launch_latent_mma<4>(a, tl, smem, st); break;
-        case 8: rc = launch_latent_mma<8>(a, tl, smem, st); break;
-        default: rc = launch_latent_mma<16>(a, tl, smem, st); break;
+        case 2: rc = launch_latent_mma<2>(a, tl, st); break;
+        case 4: rc = launch_latent_mma<4>(a, tl, st); break;
+        case 8: rc = launch_latent_mma<8>(a, tl, st); break;
+        default: rc = launch_latent_mma<16>(a, tl, st); break;
     }
     if (rc != 0) return rc;
     LAYER_CHECK_LAUNCH("dl_latent_attention_tc");

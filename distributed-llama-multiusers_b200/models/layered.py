@@ -316,9 +316,12 @@ class LayerListEngine:
         att = [mx for mx in mixers if isinstance(mx, LatentAttentionMixer)]
         self.attn_rq = 0
         if att and self.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0":
-            rq = max(1, min(16, L.LATENT_TC_ROWS // max(mx.H for mx in att)))
-            if any(L.latent_tc_supported(mx.H, mx.rank, mx.dr, self.wdtype, rq) for mx in att):
-                self.attn_rq = rq
+            # decode-sized portions: tiles of 32 stacked rows (8 warps); longer ones: 64 (16 warps, half the page visits)
+            hmax = max(mx.H for mx in att)
+            rq = max(1, min(16, 32 // hmax))
+            self._attn_rq_big = max(1, min(16, 64 // hmax))
+            if any(L.latent_tc_supported(mx.H, mx.rank, mx.dr, self.wdtype, self._attn_rq_big) for mx in att):
+                self.attn_rq = self._attn_rq_small = rq
         self.n_sms = L.sm_count()
         self._n_tiles = self._n_splits = 0
         self._attn_partial = None
@@ -505,6 +508,8 @@ class LayerListEngine:
         if self.attn_rq:
             # attention tiles: up to rq rows of one sequence at consecutive positions; few tiles (decoding) share their
             # pages among several CTAs
+            longest = max(len(r) for r in by_slot.values())
+            self.attn_rq = self._attn_rq_big if longest > self._attn_rq_small else self._attn_rq_small
             rq, to, nt, pages = self.attn_rq, self._tiles_off, 0, 1
             for s, rows in by_slot.items():
                 for i in range(0, len(rows), rq):

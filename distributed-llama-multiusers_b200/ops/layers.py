@@ -144,7 +144,7 @@ def rope_rows(x: torch.Tensor, M: int, n_heads: int, head_stride: int, offset: i
     lib.count_launch()
 
 
-LATENT_TC_ROWS = 32          # stacked (query row x head) rows of one tile of the tensor-core kernel
+LATENT_TC_ROWS = 64          # most stacked (query row x head) rows of one tile of the tensor-core kernel
 
 
 def latent_tc_supported(n_heads: int, rank: int, rot: int, cache_dtype, rq: int) -> bool:

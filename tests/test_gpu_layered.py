@@ -234,7 +234,7 @@ def test_latent_attention_tiles_of_several_rows_on_the_tensor_cores():
     holds, rows of two sequences in one batch in scrambled order, against the per-row kernel."""
     from dllama_b200.ops import layers as L
     g = torch.Generator().manual_seed(16)
-    for H, r, rot, rq in [(3, 40, 8, 10), (16, 512, 64, 2), (5, 96, 16, 6), (32, 64, 32, 1)]:
+    for H, r, rot, rq in [(3, 40, 8, 10), (16, 512, 64, 2), (5, 96, 16, 6), (32, 64, 32, 1), (16, 512, 64, 4), (3, 40, 8, 16), (40, 32, 8, 1)]:
         n_pages = 12
         cache = (torch.randn(n_pages, 32, r + rot, generator=g) * 0.5).to(torch.bfloat16).cuda()
         table = torch.stack([torch.randperm(n_pages, generator=g)[:6], torch.randperm(n_pages, generator=g)[:6]]).int().cuda()
