@@ -401,20 +401,27 @@ __global__ void __launch_bounds__(128) latent_merge_kernel(DlLatentAttnArgs a, D
     if (row < 0) return;
     const float* base = tl.partial + ((size_t)tile * tl.n_splits * LQ_MAX_ROWS + mr) * (rpad + 2);
     const size_t sstride = (size_t)LQ_MAX_ROWS * (rpad + 2);
-    float mx = -INFINITY;
-    for (int s = 0; s < tl.n_splits; ++s) mx = fmaxf(mx, base[s * sstride + rpad]);
-    float den = 0.f;
-    for (int s = 0; s < tl.n_splits; ++s) {
-        const float m = base[s * sstride + rpad];
-        if (m != -INFINITY) den += expf(m - mx) * base[s * sstride + rpad + 1];
+    // weights of the splits once, in shared memory; then every output column is a sum of independent loads
+    __shared__ float wgt[64], lsum[64];
+    const int ns = tl.n_splits;
+    if ((int)threadIdx.x < ns) {
+        wgt[threadIdx.x] = base[threadIdx.x * sstride + rpad];
+        lsum[threadIdx.x] = base[threadIdx.x * sstride + rpad + 1];
     }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int s = 0; s < ns; ++s) mx = fmaxf(mx, wgt[s]);
+    float den = 0.f;
+    for (int s = 0; s < ns; ++s) den += (wgt[s] == -INFINITY ? 0.f : expf(wgt[s] - mx)) * lsum[s];
+    __syncthreads();
+    if ((int)threadIdx.x < ns) wgt[threadIdx.x] = wgt[threadIdx.x] == -INFINITY ? 0.f : expf(wgt[threadIdx.x] - mx);
+    __syncthreads();
+    const float inv = 1.f / den;
     for (int d = threadIdx.x; d < R; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < tl.n_splits; ++s) {
-            const float m = base[s * sstride + rpad];
-            if (m != -INFINITY) acc = fmaf(expf(m - mx), base[s * sstride + d], acc);
-        }
-        a.out[((size_t)row * H + h) * R + d] = acc / den;
+#pragma unroll 8
+        for (int s = 0; s < ns; ++s) acc = fmaf(wgt[s], base[s * sstride + d], acc);
+        a.out[((size_t)row * H + h) * R + d] = acc * inv;
     }
 }
 
@@ -464,7 +471,7 @@ extern "C" int dl_latent_attention_tc(const DlLatentAttnArgs* args, const DlLate
         dl_set_error("dl_latent_attention_tc: %d heads x %d rows, rank %d + %d not supported", a.n_heads, tl.rq, a.rank, a.rot);
         return -1;
     }
-    if (tl.n_tiles < 1 || tl.n_splits < 1 || (tl.n_splits > 1 && tl.partial == nullptr)) { dl_set_error("dl_latent_attention_tc: bad tiling"); return -1; }
+    if (tl.n_tiles < 1 || tl.n_splits < 1 || tl.n_splits > 64 || (tl.n_splits > 1 && tl.partial == nullptr)) { dl_set_error("dl_latent_attention_tc: bad tiling"); return -1; }
     const int rpad = dl_latent_tc_rpad(a.rank);
     const int unit = 16 * LQ_NJ;
     int dp = (a.rank + a.rot + unit - 1) / unit * unit;

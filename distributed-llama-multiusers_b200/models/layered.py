@@ -106,6 +106,7 @@ class DenseWeight:
 
 TC_MIN_ROWS = int(os.environ.get("DLLAMA_LAYERS_TC_MIN_ROWS", "32"))
 CHUNKED_SCAN_MIN_ROWS = 256  # a batch holding this many rows of one sequence runs the recurrence chunk-parallel
+TC_HEADS_MIN_ROWS = 256      # per-head products (one small GEMM per head) take the tensor-core path from this many rows
 GRAPH_MAX_ROWS = 64          # batches up to this many rows are replayed from CUDA graphs
 
 
@@ -423,7 +424,7 @@ class LayerListEngine:
     def mm_heads(self, w: DenseWeight, x: torch.Tensor, y: torch.Tensor, M: int, x_head_stride: int, y_head_stride: int):
         """Per head h: y[:M, h*ys : h*ys+N] = x[:M, h*xs : h*xs+K] @ w[h]^T."""
         L = self.L
-        if w.wh is None or M < TC_MIN_ROWS:
+        if w.wh is None or M < TC_HEADS_MIN_ROWS:          # one batched launch (grid.z = heads) instead of two per head
             L.dense_heads(w.t, x, y, M, self.round_x, x_head_stride, y_head_stride)
             return
         for h in range(w.t.shape[0]):
