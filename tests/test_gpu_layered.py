@@ -163,6 +163,10 @@ def test_rms_norm_variants():
     rows = torch.tensor([6, 0, 3], dtype=torch.int32, device="cuda")
     L.rms_norm(x, y, 3, dim, eps, rows=rows)
     assert torch.allclose(y[:3].double(), O.rms_unit(x[[6, 0, 3]].double(), eps), atol=1e-5)
+    wide = torch.randn(2, 5000, generator=g).cuda()                          # wider than the register-cached path takes
+    yw = torch.zeros(2, 5000, device="cuda")
+    L.rms_norm(wide, yw, 2, 5000, eps)
+    assert torch.allclose(yw.double(), O.rms_unit(wide.double(), eps), atol=1e-5)
     z = x.clone()
     L.rms_norm(z, z, M, dim, eps, w=w)                                        # in place
     assert torch.allclose(z.double(), O.norm_plain(x.double(), w.double(), eps), atol=1e-5)
