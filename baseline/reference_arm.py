@@ -3,7 +3,7 @@ over loopback TCP) on the same model shape / metric and reports the same JSON li
 
 The reference is a Makefile C++ project, not a Python package, so the prescribed
 `pip install --target baseline/_ref /root/reference` cannot work ("Neither 'setup.py' nor
-'pyproject.toml' found" -- recorded in DESIGN.md).  Instead its sources are staged, byte for byte,
+'pyproject.toml' found").  Instead its sources are staged, byte for byte,
 under baseline/_ref/reference/ (git-ignored, shipped with the gpurun snapshot) and built here with
 its own Makefile (`make dllama`, g++ -O3 -march=native) in a scratch directory at run time, so the
 binary matches the CPU of the box it runs on.  None of this repo's models, kernels or engine is on

@@ -24,7 +24,7 @@
 // Independent design, not a translation: rows of a batch carry their own (position, KV slot) so that many users
 // share a forward pass (the fork's D2/D3 defects cannot occur); a batch is synchronised in one exchange instead of
 // row by row; sockets are driven by poll() so simultaneous sends cannot deadlock; the thread pool is persistent.
-// Numerics follow SURVEY Appendix A/B (same quantisation points as models/oracle.py, which is the test oracle).
+// Numerics follow the reference's rounding points (same quantisation points as models/oracle.py, which is the test oracle).
 #include <arpa/inet.h>
 #include <fcntl.h>
 #include <netdb.h>

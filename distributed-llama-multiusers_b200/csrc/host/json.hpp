@@ -205,7 +205,7 @@ private:
 };
 
 // appends `s` (UTF-8) as a quoted JSON string; invalid UTF-8 bytes become U+FFFD so the output is
-// always valid JSON (the reference's json.dump throws on them, SURVEY D6)
+// always valid JSON (the reference's json.dump throws on them)
 inline void append_quoted(std::string& o, const char* s, size_t n) {
     o.push_back('"');
     size_t i = 0;

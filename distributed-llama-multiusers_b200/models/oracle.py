@@ -1,6 +1,6 @@
 """Pure-PyTorch CPU oracle of the reference's Llama forward graph.
 
-It reproduces *where* the reference loses precision (SURVEY Appendix A/B; reference
+It reproduces *where* the reference loses precision (reference
 src/llm.cpp:126-438 and src/nn/nn-cpu-ops.cpp): Q40 weights, every matmul input cast to Q80
 (att-4, att-13, ff-4, ff-9, end-4), and -- when ``n_nodes > 1`` -- every per-node partial sum of
 wo/w2 cast to Q80 before the merge-add (att-15, ff-11).  Residual stream, norms, RoPE, KV cache,

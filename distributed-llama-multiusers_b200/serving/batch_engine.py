@@ -1,7 +1,7 @@
 """Continuous-batching generation loop: many concurrent requests share every forward pass.
 
 This is the *intended* behaviour of the fork's ``inference_loop`` (src/app.cpp:314-402) without its
-defects (SURVEY 2.9 D1-D4, D6): each request keeps its own prompt (prefilled in chunks), position,
+defects: each request keeps its own prompt (prefilled in chunks), position,
 KV slot, sampler (temperature / top-p / seed per request), streaming UTF-8 decoder and stop
 detector; a finished request leaves the batch and a waiting one joins at the next step.  Batch
 formation lives in the C++ scheduler (csrc/host/scheduler.cpp); this module drives the GPU engine,

@@ -1,6 +1,6 @@
 """Native CPU backend (csrc/host/cpu_backend.cpp): codecs and kernels against the NumPy twins and the reference's
 published goldens, the engine against the PyTorch oracle, and root + workers over loopback TCP (workers without a
-model file) against the single-node run -- the distributed test the reference does not have (SURVEY 4)."""
+model file) against the single-node run -- the distributed test the reference does not have."""
 import socket
 import threading
 import time
