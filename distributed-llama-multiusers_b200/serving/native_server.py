@@ -61,8 +61,11 @@ class NativeApiServer:
                                                   self._h_params[1], self._h_params[2]))
         self._lf, self._ns, self._greedy, self._nrel = C.c_int(0), C.c_int(0), C.c_int(0), C.c_int(0)
         if self._device_sampler:
-            from ..ops import kernels as _K
-            self._K = _K
+            # an engine with a kernel library of its own brings its binding of the sampler
+            self._sample_rows = getattr(engine, "sample_rows", None)
+            if self._sample_rows is None:
+                from ..ops import kernels as _K
+                self._sample_rows = _K.sample_rows
             self._d_params = torch.zeros(3, R, dtype=torch.float32, device=dev)
             self._d_tok = torch.zeros(R, dtype=torch.int32, device=dev)
         else:
@@ -167,7 +170,7 @@ class NativeApiServer:
         elif self._device_sampler:
             logits = eng.forward(toks, pos, slots, logits_from=lf)
             self._d_params.copy_(self._h_params, non_blocking=True)
-            self._K.sample_rows(logits[:n_s], self._d_params[0], self._d_params[1], self._d_params[2], self._d_tok)
+            self._sample_rows(logits[:n_s], self._d_params[0], self._d_params[1], self._d_params[2], self._d_tok)
             self._h_tok.copy_(self._d_tok, non_blocking=True)
             torch.cuda.current_stream().synchronize()
             rc = L.dl_srv_commit(h, n_s, self._h_tok.data_ptr())

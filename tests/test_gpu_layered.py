@@ -524,3 +524,56 @@ def test_the_command_line_serves_a_model_directory(model_a, tmp_path, capsys):
     s = eng.alloc_slot()
     lg = eng.prefill(s, reqs[2])
     _assert_close(lg.cpu(), want[2][-1:], F32_TOL, "prefill() of the engine surface")
+
+
+def test_the_http_server_serves_a_model_directory(tmp_path):
+    """`dllama-api`'s native front end (C++ HTTP server and scheduler) on the layer-list engine: concurrent greedy
+    and sampled chat completions, the same seed twice, a streamed answer."""
+    import json
+    import threading
+    import urllib.request
+    from dllama_b200.formats import tfile
+    from dllama_b200.models.layered import example_config, write_random_model
+    from dllama_b200.serving import api_types as A
+    from dllama_b200.serving.native_server import NativeApiServer
+    from dllama_b200.text import native as T
+    d = str(tmp_path / "m")
+    write_random_model(d, example_config(width=128, vocab=1024, blocks=3, heads=4), seed=23)
+    tp = str(tmp_path / "t.t")
+    tfile.write_synthetic_tokenizer(tp, 1024)
+    tok = T.Tokenizer(tp)
+    eng = _engine(d, "bfloat16", max_rows=64, n_slots=6, seq=256)
+    srv = NativeApiServer(eng, tok, "m", A.InferenceParams(messages=[], temperature=0.0, top_p=0.9, seed=1), host="127.0.0.1",
+                          port=0, verbose=False)
+    srv.start()
+
+    def post(body):
+        req = urllib.request.Request(f"http://127.0.0.1:{srv.port}/v1/chat/completions", data=json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"}, method="POST")
+        with urllib.request.urlopen(req, timeout=120) as r:
+            return r.read().decode("utf-8")
+
+    try:
+        out = {}
+        texts = ["hello world", "the of and hello world token model fast " * 3, "token"]
+        ts = [threading.Thread(target=lambda i=i: out.__setitem__(i, json.loads(post(
+            {"messages": [{"role": "user", "content": texts[i]}], "max_tokens": 5})))) for i in range(3)]
+        [t.start() for t in ts]
+        [t.join(timeout=200) for t in ts]
+        sampled = [json.loads(post({"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 1.0,
+                                    "top_p": 0.95, "seed": 7})) for _ in range(2)]
+        again = json.loads(post({"messages": [{"role": "user", "content": texts[0]}], "max_tokens": 5}))
+        assert len(out) == 3 and srv.stats()["engine_errors"] == 0
+        for r in list(out.values()) + sampled:
+            assert r["object"] == "chat.completion" and r["usage"]["completion_tokens"] >= 1
+        assert sampled[0]["choices"][0]["message"]["content"] == sampled[1]["choices"][0]["message"]["content"]
+        assert again["choices"][0]["message"]["content"] == out[0]["choices"][0]["message"]["content"]
+        raw = post({"messages": [{"role": "user", "content": texts[0]}], "max_tokens": 5, "stream": True})
+        streamed = "".join(json.loads(e[6:])["choices"][0]["delta"].get("content", "")
+                           for e in raw.split("\r\n\r\n") if e.startswith("data: {"))
+        assert streamed == out[0]["choices"][0]["message"]["content"]
+        st = srv.stats()
+        assert st["running"] == 0 and st["waiting"] == 0 and st["free_slots"] == 6
+    finally:
+        srv.close()
+        eng.close()
