@@ -419,7 +419,7 @@ def layered_config(sz: dict, n_layers: int, vocab: int) -> dict:
             mixer = {"heads": sz["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": sz["q_rank"],
                      "kv_rank": sz["kv_rank"], "scale": 1.0 / math.sqrt(192.0), "rot": {"base": 10000.0, "dims": 64}}
             if i >= 5:
-                mixer["kv_from"] = 3
+                mixer["kv_from"] = 1
             layers.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": sz["ff"]}})
     return {"architecture": "Ribivik", "width": sz["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
             "layers": layers}

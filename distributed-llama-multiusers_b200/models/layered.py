@@ -691,16 +691,16 @@ def write_random_model(model_dir: str, config: dict, seed: int = 0) -> Dict[str,
 
 
 def example_config(width: int = 192, vocab: int = 320, blocks: int = 2, heads: int = 4) -> dict:
-    """A small Ribivik-shaped configuration: `blocks` x (mamba2 layer without feed-forward, latent-attention layer
-    with one); from the third attention layer on, layers read the cache of the second."""
+    """A small Ribivik-shaped configuration: `blocks` x (latent-attention layer with a feed-forward, mamba2 layer, every
+    second of them with a narrow feed-forward of its own); attention layers after the first read the first one's cache."""
     layers = []
     for b in range(blocks):
-        layers.append({"type": "mamba2", "mlp": None,
-                       "mixer": {"heads": heads, "vdim": 24, "state": 16, "groups": 2, "conv": 3, "norm_groups": 2}})
         mixer = {"heads": heads, "dim": 40, "rot_dim": 8, "vdim": 24, "q_rank": 48, "kv_rank": 56,
                  "scale": 1.0 / math.sqrt(48), "rot": {"base": 10000.0, "dims": 8}}
-        if b >= 2:
-            mixer["kv_from"] = 3
+        if b >= 1:
+            mixer["kv_from"] = 0
         layers.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": 2 * width}})
+        layers.append({"type": "mamba2", "mlp": {"kind": "dense", "ff": width // 2} if b % 2 else None,
+                       "mixer": {"heads": heads, "vdim": 24, "state": 16, "groups": 2, "conv": 3, "norm_groups": 2}})
     return {"architecture": "Ribivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 25.0,
             "layers": layers}

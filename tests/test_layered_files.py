@@ -40,9 +40,9 @@ def test_configuration_and_registry(tmp_path):
     assert registry.is_model_dir(d) and not registry.is_model_dir(str(tmp_path / "nope"))
     assert registry.architecture_of(d) == "Ribivik" and "Ribivik" in registry.ARCHITECTURES
     c = LayerListConfig.load(d)
-    assert c.vocab_size == cfg["vocab"] and c.n_layers == 6 and c.layers[0].mlp is None and c.layers[5].mixer["kv_from"] == 3
-    assert "l5.mix.dkv" not in tensors and "l3.mix.dkv" in tensors and "l0.mlp.up" not in tensors
-    assert tensors["l0.mix.in"].shape == (2 * 96 + 2 * 2 * 16 + 4, 192) and tensors["l1.mix.uq"].shape == (4 * 48, 48)
+    assert c.vocab_size == cfg["vocab"] and c.n_layers == 6 and c.layers[1].mlp is None and c.layers[4].mixer["kv_from"] == 0
+    assert "l4.mix.dkv" not in tensors and "l0.mix.dkv" in tensors and "l1.mlp.up" not in tensors and "l3.mlp.up" in tensors
+    assert tensors["l1.mix.in"].shape == (2 * 96 + 2 * 2 * 16 + 4, 192) and tensors["l0.mix.uq"].shape == (4 * 48, 48)
     with open(os.path.join(d, "config.json"), "w") as f:
         json.dump({**cfg, "architecture": "NoSuchDesign"}, f)
     with pytest.raises(ValueError):
