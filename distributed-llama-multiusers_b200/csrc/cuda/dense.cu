@@ -20,19 +20,25 @@ __device__ __forceinline__ float dense_epi(float acc, int epi, float aux, float 
 }
 
 // ------------------------------------------------------------------------------------------------
-// embedding gather: x[m] = table[tokens[m]]
+// embedding gather: x[m][c] = scale * table[tokens[m]] for each of `copies` copies of the row (row layout [copies][dim])
 // ------------------------------------------------------------------------------------------------
 template <typename WT>
-__global__ void embed_rows_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int dim) {
+__global__ void embed_rows_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int dim,
+                                  float scale, int copies) {
     const int m = blockIdx.x;
     const WT* src = table + (size_t)tokens[m] * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) x[(size_t)m * dim + i] = ld_f(src + i);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = ld_f(src + i) * scale;
+        for (int c = 0; c < copies; ++c) x[((size_t)m * copies + c) * dim + i] = v;
+    }
 }
 
-extern "C" int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, void* stream) {
+extern "C" int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, float scale, int copies,
+                             void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
-    if (wtype == DL_T_BF16) embed_rows_kernel<<<M, 128, 0, st>>>((const __nv_bfloat16*)table, tokens, x, dim);
-    else embed_rows_kernel<<<M, 128, 0, st>>>((const float*)table, tokens, x, dim);
+    if (copies < 1) { dl_set_error("dl_embed_rows: copies < 1"); return -1; }
+    if (wtype == DL_T_BF16) embed_rows_kernel<<<M, 128, 0, st>>>((const __nv_bfloat16*)table, tokens, x, dim, scale, copies);
+    else embed_rows_kernel<<<M, 128, 0, st>>>((const float*)table, tokens, x, dim, scale, copies);
     LAYER_CHECK_LAUNCH("dl_embed_rows");
     return 0;
 }

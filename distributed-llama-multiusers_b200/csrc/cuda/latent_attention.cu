@@ -10,7 +10,7 @@
 // a slice of each head of a row-major activation, and the attention itself over the paged latent cache, one CTA per
 // query row with every head of the row sharing each page it stages in shared memory.  Softmax, norms and rotary
 // angles are f32 (angles in f64); the cache is bf16 or f32.
-#include "layer_common.cuh"
+#include "mma_common.cuh"
 #include "../../../include/dllama_b200.h"
 
 // rotate-half layout: dimension i pairs with i + dims/2; (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = pos * f_i
@@ -62,23 +62,25 @@ extern "C" int dl_latent_kv_write(const DlLatentKvArgs* args, int M, void* strea
 // rotary on dims [offset, offset + rope_dims) of each head of x[M][n_heads][head_stride], in place
 // ------------------------------------------------------------------------------------------------
 __global__ void rope_rows_kernel(float* x, long long ld, int n_heads, int head_stride, int offset, int rope_dims,
-                                 const double* __restrict__ freqs, const int* __restrict__ pos) {
+                                 const double* __restrict__ freqs, const int* __restrict__ pos, int interleaved, float mag) {
     const int m = blockIdx.x, half = rope_dims / 2;
     const int p = pos[m];
     for (int t = threadIdx.x; t < n_heads * half; t += blockDim.x) {
         const int h = t / half, i = t % half;
         float* q = x + (size_t)m * ld + (size_t)h * head_stride + offset;
+        const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
         float u, v;
-        rot_pair(q[i], q[i + half], p, freqs[i], u, v);
-        q[i] = u;
-        q[i + half] = v;
+        rot_pair(q[iu], q[iv], p, freqs[i], u, v);
+        q[iu] = u * mag;
+        q[iv] = v * mag;
     }
 }
 
+// interleaved: dimension 2i pairs with 2i + 1 (else i with i + dims/2); mag multiplies cos and sin (1: a pure rotation)
 extern "C" int dl_rope_rows(float* x, long long ld, int M, int n_heads, int head_stride, int offset, int rope_dims,
-                            const double* freqs, const int* pos, void* stream) {
+                            const double* freqs, const int* pos, int interleaved, float mag, void* stream) {
     if ((rope_dims & 1) || offset + rope_dims > head_stride) { dl_set_error("dl_rope_rows: bad rotary size"); return -1; }
-    rope_rows_kernel<<<M, 128, 0, (cudaStream_t)stream>>>(x, ld, n_heads, head_stride, offset, rope_dims, freqs, pos);
+    rope_rows_kernel<<<M, 128, 0, (cudaStream_t)stream>>>(x, ld, n_heads, head_stride, offset, rope_dims, freqs, pos, interleaved, mag);
     LAYER_CHECK_LAUNCH("dl_rope_rows");
     return 0;
 }
@@ -186,25 +188,6 @@ extern "C" int dl_latent_attention(const DlLatentAttnArgs* args, int M, void* st
 #define LQ_MAX_ROWS 64
 #define LQ_NJ 4
 #define LQ_SP_LD 34                       // even: partial scores move as float2
-
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem_row) {
-    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem_row);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sa));
-}
-__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 
 // NT: n-tiles (8 columns) of O per column-warp; the kernel covers rank <= NT * 8 * LQ_NJ.  NI: row tiles of 16.
 template <int NT, int NI>

@@ -1,0 +1,186 @@
+// Routed experts: every token runs `top` of `experts` small feed-forward layers  W_down act(W_up h),  act = relu(.)^2,
+// and sums their outputs weighted by the router's scores.
+//
+// Routing (dl_moe_select), from the router logits z[M][experts] (a dense product, f32):  s = sigmoid(z).  The experts
+// form `groups` equal groups of neighbours; a group's score is the sum of its `group_top` largest scores and only the
+// `keep` best groups stay eligible; the `top` eligible experts with the largest scores are chosen, their weights are
+// their scores (divided by the sum of the chosen scores if `renorm`).  Ties go to the lower index.  groups = keep = 1
+// is plain top-k routing.
+//
+// Expert products, two forms:
+//   * per (row, chosen expert) pair, weight-streaming (dl_moe_rows: f32 weights at any size, bf16 weights for
+//     decode-sized batches): up-projection + relu^2 into act[M * top][ff], then one warp per output column does the
+//     `top` down-projections of a row and their weighted sum in the order the experts were chosen;
+//   * grouped for the tensor cores (dl_moe_plan / dl_moe_combine around the grouped tcgen05 GEMM of gemm_wh_tc.cu):
+//     the (row, expert) pairs are sorted by expert into segments padded to 8 rows, the rows are gathered into the
+//     GEMM's activation image, one grouped GEMM per projection runs all experts, and the combine kernel sums each
+//     row's `top` results with its weights, in the order chosen -- a row's result does not depend on the batch.
+// All expert weights of a layer are stacked: w_up [experts][ff][width], w_down [experts][width][ff].
+#include "layer_common.cuh"
+#include "../../../include/dllama_b200.h"
+
+// ------------------------------------------------------------------------------------------------
+// routing: one warp per row; scores in shared memory, selection by lane 0 (experts and top are small)
+// ------------------------------------------------------------------------------------------------
+#define MS_WARPS 4
+
+__global__ void __launch_bounds__(MS_WARPS * 32) moe_select_kernel(DlMoeSelectArgs a) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.x * MS_WARPS + warp;
+    if (m >= a.M) return;
+    const int E = a.experts, per = E / a.groups;
+    float* s = sm + (size_t)warp * (E + a.groups);        // [E] scores, then [groups] group scores (< 0: dropped)
+    float* gs = s + E;
+    for (int e = lane; e < E; e += 32) s[e] = sigmoid_f(a.z[(size_t)m * a.ldz + e]);
+    __syncwarp();
+    for (int g = lane; g < a.groups; g += 32) {            // sum of the group's largest scores
+        float sum = 0.f, prev_v = INFINITY;
+        int prev_i = -1;
+        for (int k = 0; k < a.group_top && k < per; ++k) {      // next in the order (score down, index up)
+            int best = -1;
+            for (int i = 0; i < per; ++i) {
+                const float v = s[g * per + i];
+                const bool after_prev = v < prev_v || (v == prev_v && i > prev_i);
+                if (after_prev && (best < 0 || v > s[g * per + best])) best = i;
+            }
+            prev_v = s[g * per + best];
+            prev_i = best;
+            sum += prev_v;
+        }
+        gs[g] = sum;
+    }
+    __syncwarp();
+    if (lane == 0) {
+        // keep the best groups: mark the others
+        const int drop = a.groups - a.keep;
+        for (int k = 0; k < drop; ++k) {
+            int worst = -1;
+            for (int g = 0; g < a.groups; ++g)
+                if (gs[g] >= 0.f && (worst < 0 || gs[g] <= gs[worst])) worst = g;      // ties: the higher index goes first
+            gs[worst] = -1.f;
+        }
+        float total = 0.f;
+        for (int k = 0; k < a.top; ++k) {
+            int best = -1;
+            for (int e = 0; e < E; ++e)
+                if (gs[e / per] >= 0.f && s[e] >= 0.f && (best < 0 || s[e] > s[best])) best = e;
+            a.sel[(size_t)m * a.top + k] = best;
+            a.wgt[(size_t)m * a.top + k] = s[best];
+            total += s[best];
+            s[best] = -1.f;                                // sigmoid scores are >= 0: taken
+        }
+        if (a.renorm)
+            for (int k = 0; k < a.top; ++k) a.wgt[(size_t)m * a.top + k] /= total;
+    }
+}
+
+extern "C" int dl_moe_select(const DlMoeSelectArgs* args, void* stream) {
+    const DlMoeSelectArgs& a = *args;
+    if (a.M < 1 || a.experts < 1 || a.groups < 1 || a.experts % a.groups || a.keep < 1 || a.keep > a.groups || a.top < 1 ||
+        a.top > a.keep * (a.experts / a.groups) || a.group_top < 1) {
+        dl_set_error("dl_moe_select: %d experts in %d groups, keep %d, top %d", a.experts, a.groups, a.keep, a.top);
+        return -1;
+    }
+    const size_t smem = (size_t)MS_WARPS * (a.experts + a.groups) * sizeof(float);
+    if (smem > 48 * 1024) { dl_set_error("dl_moe_select: too many experts (%d)", a.experts); return -1; }
+    moe_select_kernel<<<(a.M + MS_WARPS - 1) / MS_WARPS, MS_WARPS * 32, smem, (cudaStream_t)stream>>>(a);
+    LAYER_CHECK_LAUNCH("dl_moe_select");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// per-pair products: a warp per output column, lanes stride K (16-byte loads where the rows allow)
+// ------------------------------------------------------------------------------------------------
+template <typename WT> struct MoeVec;
+template <> struct MoeVec<float> {
+    static __device__ __forceinline__ void load8(const float* p, float* o) {
+        const float4 u = *reinterpret_cast<const float4*>(p), v = *reinterpret_cast<const float4*>(p + 4);
+        o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w; o[4] = v.x; o[5] = v.y; o[6] = v.z; o[7] = v.w;
+    }
+};
+template <> struct MoeVec<__nv_bfloat16> {
+    static __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* o) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const uint32_t r[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            o[2 * i] = __uint_as_float(r[i] << 16);
+            o[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u);
+        }
+    }
+};
+
+// sum_k w[k] x[k] over the warp (every lane gets it); vec: K % 8 == 0 and both rows 16-byte aligned
+template <typename WT, bool RX>
+__device__ __forceinline__ float warp_dot(const WT* __restrict__ w, const float* __restrict__ x, int K, bool vec, int lane) {
+    float acc = 0.f;
+    if (vec) {
+        for (int k = lane * 8; k < K; k += 256) {
+            float wv[8], xv[8];
+            MoeVec<WT>::load8(w + k, wv);
+            MoeVec<float>::load8(x + k, xv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(RX ? round_bf16(xv[i]) : xv[i], wv[i], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(RX ? round_bf16(x[k]) : x[k], ld_f(w + k), acc);
+    }
+    return warp_sum(acc);
+}
+
+#define MR_WARPS 8
+
+template <typename WT, bool RX>
+__global__ void __launch_bounds__(MR_WARPS * 32) moe_up_rows_kernel(DlMoeArgs a, bool vec) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pair = blockIdx.x, f = blockIdx.y * MR_WARPS + warp;
+    if (f >= a.ff) return;
+    const int m = pair / a.top, e = a.sel[pair];
+    const WT* w = (const WT*)a.w_up + ((size_t)e * a.ff + f) * a.width;
+    const float v = warp_dot<WT, RX>(w, a.x + (size_t)m * a.ldx, a.width, vec, lane);
+    if (lane == 0) {
+        const float r = fmaxf(v, 0.f);
+        a.act[(size_t)pair * a.ff + f] = r * r;
+    }
+}
+
+template <typename WT, bool RX>
+__global__ void __launch_bounds__(MR_WARPS * 32) moe_down_rows_kernel(DlMoeArgs a, bool vec) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.x, c = blockIdx.y * MR_WARPS + warp;
+    if (c >= a.width) return;
+    float out = 0.f;
+    for (int k = 0; k < a.top; ++k) {
+        const int pair = m * a.top + k, e = a.sel[pair];
+        const WT* w = (const WT*)a.w_down + ((size_t)e * a.width + c) * a.ff;
+        out = fmaf(a.wgt[pair], warp_dot<WT, RX>(w, a.act + (size_t)pair * a.ff, a.ff, vec, lane), out);
+    }
+    if (lane == 0) a.y[(size_t)m * a.ldy + c] = out;
+}
+
+template <typename WT, bool RX>
+static void launch_moe_rows(const DlMoeArgs& a, cudaStream_t st) {
+    const bool al = ((uintptr_t)a.w_up & 15) == 0 && ((uintptr_t)a.w_down & 15) == 0 && ((uintptr_t)a.x & 15) == 0 && ((uintptr_t)a.act & 15) == 0;
+    const bool vec_up = al && a.width % 8 == 0 && a.ldx % 4 == 0, vec_down = al && a.ff % 8 == 0;
+    moe_up_rows_kernel<WT, RX><<<dim3(a.M * a.top, (a.ff + MR_WARPS - 1) / MR_WARPS), MR_WARPS * 32, 0, st>>>(a, vec_up);
+    moe_down_rows_kernel<WT, RX><<<dim3(a.M, (a.width + MR_WARPS - 1) / MR_WARPS), MR_WARPS * 32, 0, st>>>(a, vec_down);
+}
+
+extern "C" int dl_moe_rows(const DlMoeArgs* args, void* stream) {
+    const DlMoeArgs& a = *args;
+    if (a.M < 1 || a.width < 1 || a.ff < 1 || a.top < 1) { dl_set_error("dl_moe_rows: empty problem"); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a.wtype == DL_T_BF16) {
+        if (a.round_x) launch_moe_rows<__nv_bfloat16, true>(a, st);
+        else launch_moe_rows<__nv_bfloat16, false>(a, st);
+    } else if (a.wtype == DL_T_F32) {
+        if (a.round_x) launch_moe_rows<float, true>(a, st);
+        else launch_moe_rows<float, false>(a, st);
+    } else {
+        dl_set_error("dl_moe_rows: unknown weight type %d", a.wtype);
+        return -1;
+    }
+    LAYER_CHECK_LAUNCH("dl_moe_rows");
+    return 0;
+}

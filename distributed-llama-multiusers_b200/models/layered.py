@@ -1,7 +1,10 @@
 """GPU engine for layer-list models: a model directory (config.json + model.safetensors) whose configuration lists its
-layers one by one, each a token mixer followed by an optional feed-forward, with dense bf16 weights.
+layers one by one, each a token mixer followed by an optional feed-forward, with dense bf16 weights.  How a sublayer
+meets the residual stream is the architecture's ``residual`` style (``RESIDUAL_STYLES``), everything in f32:
 
-    x <- x + post_norm(mixer(pre_norm(x)));   x <- x + post_norm(ff(pre_norm(x)))      per layer, residual in f32
+    "sandwich":  x <- x + post_norm(sub(pre_norm(x)))                    norm weights stored around zero (Ribivik)
+    "hyper":     u = sum_s in[s] x_s;  y = sub(norm(u));  x_t <- sum_s mix[s][t] x_s + m out[t] y      (Sunesun)
+                 `streams` copies of the stream (hyper-connections); without them the plain x <- x + m sub(norm(x))
 
 The mixers and feed-forwards are looked up by name (``MIXERS`` / ``FEED_FORWARDS`` below), so another design composes
 the same mechanisms with its own sizes and order; ``ARCHITECTURES`` in models/registry.py maps an architecture name to
@@ -9,7 +12,13 @@ this engine.  Mixers here:
 
 * ``latent_attention`` -- attention whose keys and values are up-projections of one small cached latent per token plus
   a rotated key part shared by all heads; a layer may read the cache another layer writes (``kv_from``);
-* ``mamba2`` -- a gated selective state-space recurrence with a short causal convolution in front.
+* ``mamba2`` -- a gated selective state-space recurrence with a short causal convolution in front;
+* ``attention`` -- grouped-query attention over a sliding window whose values are its keys (one projection, one cache
+  line per token and key/value head), interleaved rotary positions with optional frequency interpolation, soft-capped
+  scores.
+
+Feed-forwards: ``dense`` and ``moe`` (sigmoid-scored, group-limited routing over small squared-ReLU experts).  A layer
+with ``weights_of: j`` runs layer j's weights on a cache or state of its own (a looped layer).
 
 What the engine shares with ``LlamaEngine`` is the serving surface (slots, rows with per-row positions, paged token
 cache from ``PageAllocator``, ``forward`` / ``decode_step_greedy`` / ``prefill``), so the scheduler, the batching loop
@@ -43,6 +52,11 @@ class LayerSpec:
     type: str
     mixer: dict
     mlp: Optional[dict]
+    weights_of: Optional[int] = None       # run that layer's weights (norms, mixer, feed-forward) on a cache / state of its own
+
+
+# how sublayers meet the residual stream, by architecture name
+RESIDUAL_STYLES = {"Ribivik": "sandwich", "Sunesun": "hyper"}
 
 
 @dataclass
@@ -54,6 +68,11 @@ class LayerListConfig:
     logit_softcap: float
     layers: List[LayerSpec] = field(default_factory=list)
     seq_len: int = 0
+    residual: str = "sandwich"
+    embed_scale: float = 1.0               # the embedding output is multiplied by it
+    residual_mult: float = 1.0             # "hyper": every sublayer output is multiplied by it on its way into the stream
+    streams: int = 1                       # "hyper": copies of the residual stream
+    hyper_weights: bool = False            # the layers bring hc<q>.in / .out / .mix tensors (else the plain sum)
 
     # the serving code reads these names from every engine's header
     @property
@@ -66,10 +85,18 @@ class LayerListConfig:
 
     @staticmethod
     def from_dict(c: dict) -> "LayerListConfig":
-        layers = [LayerSpec(l["type"], dict(l["mixer"]), dict(l["mlp"]) if l.get("mlp") else None) for l in c["layers"]]
-        return LayerListConfig(architecture=c["architecture"], width=int(c["width"]), vocab=int(c["vocab"]),
+        layers = [LayerSpec(l["type"], dict(l["mixer"]), dict(l["mlp"]) if l.get("mlp") else None,
+                            int(l["weights_of"]) if l.get("weights_of") is not None else None) for l in c["layers"]]
+        for i, l in enumerate(layers):
+            if l.weights_of is not None and (not 0 <= l.weights_of < len(layers) or layers[l.weights_of].weights_of is not None):
+                raise ValueError(f"layer {i}: weights_of {l.weights_of} is not a layer with weights of its own")
+        arch = c["architecture"]
+        return LayerListConfig(architecture=arch, width=int(c["width"]), vocab=int(c["vocab"]),
                                norm_eps=float(c["norm"]["eps"]), logit_softcap=float(c.get("logit_softcap") or 0.0),
-                               layers=layers)
+                               layers=layers, residual=RESIDUAL_STYLES.get(arch, "sandwich"),
+                               embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)),
+                               residual_mult=float(c.get("residual_mult", 1.0)),
+                               streams=int(c.get("streams") or 1), hyper_weights=bool(c.get("streams")))
 
     @staticmethod
     def load(model_dir: str) -> "LayerListConfig":
@@ -86,6 +113,26 @@ def rotary_frequencies(base: float, dims: int) -> torch.Tensor:
     """f_i = base^(-2 i / dims), i < dims / 2, in f64 (the kernels form pos * f_i in f64)."""
     i = torch.arange(dims // 2, dtype=torch.float64)
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dims)
+
+
+def interpolated_rotary(base: float, dims: int, scaling: Optional[dict]):
+    """(frequencies f64 [dims / 2], magnitude).  Without `scaling`: the plain f_i and 1.  With scaling {factor, original,
+    fast, slow} the slow frequencies are divided by `factor`, the fast ones kept and those between blended (YaRN):
+    with d(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), dims - 1),
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):  f_i' = f_i / factor * r_i + f_i (1 - r_i); cos and sin are
+    multiplied by 0.1 ln(factor) + 1."""
+    f = rotary_frequencies(base, dims)
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def d(t):
+        return dims * math.log(original / (2.0 * math.pi * float(t))) / (2.0 * math.log(base))
+
+    lo, hi = max(math.floor(d(scaling["fast"])), 0), min(math.ceil(d(scaling["slow"])), dims - 1)
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    r = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * r + f * (1.0 - r), 0.1 * math.log(factor) + 1.0
 
 
 class DenseWeight:
@@ -247,24 +294,147 @@ class DenseFeedForward:
         e.mm(self.w_down, up, y, M)
 
 
-MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer}
-FEED_FORWARDS = {"dense": DenseFeedForward}
+class WindowAttentionMixer:
+    """Tensors <prefix>q, k, o.  Sizes: heads, kv_heads, dim (per-head query / key size), vdim (= dim: the values are the
+    keys as projected, there is no value projection), scale, softcap (0 / absent: none), mask.size (the window: a
+    position sees itself and the size - 1 before it; absent: everything before it), rot {base, dims, scaling}.
+    The cache holds one line per token and key/value head: the rotated key followed by the unrotated head of k."""
+
+    def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str, share: Optional["WindowAttentionMixer"] = None):
+        self.eng, self.index = eng, index
+        self.H, self.G, self.dim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
+        if int(m.get("vdim", self.dim)) != self.dim:
+            raise ValueError(f"layer {index}: the values are the keys, so vdim must equal dim")
+        if self.H % self.G:
+            raise ValueError(f"layer {index}: {self.H} heads do not divide into {self.G} key/value heads")
+        self.scale, self.softcap = float(m["scale"]), float(m.get("softcap") or 0.0)
+        self.window = int((m.get("mask") or {}).get("size") or 0)
+        rot = m.get("rot") or {"base": 10000.0, "dims": 0}
+        self.rope_dims = int(rot["dims"])
+        if self.rope_dims > self.dim or self.rope_dims % 2:
+            raise ValueError(f"layer {index}: rotary dims {self.rope_dims} do not fit dim {self.dim}")
+        freqs, self.rope_mag = interpolated_rotary(float(rot["base"]), self.rope_dims, rot.get("scaling"))
+        self.freqs = freqs.to(eng.device) if self.rope_dims else torch.zeros(1, dtype=torch.float64, device=eng.device)
+        if share is None:
+            W, D = eng.weight, eng.dense_weight
+            wq, wk = W(prefix + "q"), W(prefix + "k")
+            if tuple(wq.shape) != (self.H * self.dim, eng.cfg.width) or tuple(wk.shape) != (self.G * self.dim, eng.cfg.width):
+                raise ValueError(f"layer {index}: q / k have shapes {tuple(wq.shape)} / {tuple(wk.shape)}")
+            self.w_qk = D(torch.cat([wq, wk], 0).contiguous())         # one product for queries and keys
+            self.w_o = D(W(prefix + "o"))
+        else:
+            self.w_qk, self.w_o = share.w_qk, share.w_o
+        self.owns_weights = share is None
+        self.line = self.dim + self.rope_dims
+        self.cache = torch.zeros(eng.n_pages, self.G, PAGE, self.line, dtype=eng.wdtype, device=eng.device)
+
+    def scratch(self) -> Dict[str, int]:
+        return {"qk": (self.H + self.G) * self.dim, "o": self.H * self.dim}
+
+    def bind(self, mixers: list):
+        pass
+
+    def weight_bytes(self) -> int:
+        return self.w_qk.nbytes() + self.w_o.nbytes() if self.owns_weights else 0
+
+    def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
+        e, L = self.eng, self.eng.L
+        H, G, d, rd = self.H, self.G, self.dim, self.rope_dims
+        qk, o = e.buf("qk", (H + G) * d), e.buf("o", H * d)
+        e.mm(self.w_qk, h, qk, M, src="h")
+        if rd:
+            L.rope_rows(qk, M, H, d, 0, rd, self.freqs, e.pos, interleaved=True, mag=self.rope_mag)
+        L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache)
+        L.window_attention(qk, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
+                           self.cache)
+        e.mm(self.w_o, o, y, M)
+
+
+class RoutedExperts:
+    """Tensors <prefix>router, e<n>.up, e<n>.down.  Sizes: expert.ff, router {experts, top, groups {count, keep}}.
+    Router scores are sigmoid(W_router h) in f32; experts form `count` groups of neighbours scored by the sum of their
+    two largest scores, only the `keep` best groups are eligible; the `top` best eligible experts run and their outputs
+    are summed with their scores as weights (not renormalised)."""
+
+    def __init__(self, eng: "LayerListEngine", index: int, m: dict, prefix: str):
+        self.eng = eng
+        r = m["router"]
+        self.E, self.top, self.ff = int(r["experts"]), int(r["top"]), int(m["expert"]["ff"])
+        g = r.get("groups") or {"count": 1, "keep": 1}
+        self.groups, self.keep = int(g["count"]), int(g["keep"])
+        if self.E % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.keep * (self.E // self.groups):
+            raise ValueError(f"layer {index}: {self.E} experts, {self.groups} groups (keep {self.keep}), top {self.top}")
+        self.router = eng.dense_weight(eng.weight(prefix + "router"))
+        self.w_up = torch.stack([eng.weight(f"{prefix}e{n}.up") for n in range(self.E)]).contiguous()        # [E][ff][W]
+        self.w_down = torch.stack([eng.weight(f"{prefix}e{n}.down") for n in range(self.E)]).contiguous()    # [E][W][ff]
+        if tuple(self.w_up.shape) != (self.E, self.ff, eng.cfg.width) or tuple(self.w_down.shape) != (self.E, eng.cfg.width, self.ff):
+            raise ValueError(f"layer {index}: expert weights have shapes {tuple(self.w_up.shape)} / {tuple(self.w_down.shape)}")
+        eng._kmax = max(eng._kmax, self.ff, eng.cfg.width)
+
+    def scratch(self) -> Dict[str, int]:
+        return {"router_z": self.E, "moe_act": self.top * self.ff, "moe_sel": self.top, "moe_wgt": self.top}
+
+    def weight_bytes(self) -> int:
+        return self.router.nbytes() + (self.w_up.numel() + self.w_down.numel()) * self.w_up.element_size()
+
+    def forward(self, h: torch.Tensor, y: torch.Tensor, M: int):
+        e, L = self.eng, self.eng.L
+        z, act = e.buf("router_z", self.E), e.buf("moe_act", self.top * self.ff)
+        sel, wgt = e.buf("moe_sel", self.top).view(torch.int32), e.buf("moe_wgt", self.top)
+        e.mm(self.router, h, z, M, src="h")
+        L.moe_select(z, M, self.E, self.top, self.groups, self.keep, sel, wgt)
+        L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x)
+
+
+MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer, "attention": WindowAttentionMixer}
+FEED_FORWARDS = {"dense": DenseFeedForward, "moe": RoutedExperts}
+
+
+class _HyperWeights:
+    """Read / write weights of one sublayer's hyper-connection: in [S], out [S], mix [S][S] (from, to), f32."""
+
+    def __init__(self, eng: "LayerListEngine", prefix: Optional[str]):
+        S = eng.cfg.streams
+        if prefix is None:                      # the plain residual sum
+            ones = torch.ones(S, dtype=torch.float32, device=eng.device)
+            self.w_in, self.w_out, self.mix = ones, ones.clone(), torch.eye(S, dtype=torch.float32, device=eng.device).contiguous()
+        else:
+            self.w_in, self.w_out, self.mix = eng.vector(prefix + "in"), eng.vector(prefix + "out"), eng.vector(prefix + "mix")
+            if tuple(self.w_in.shape) != (S,) or tuple(self.w_out.shape) != (S,) or tuple(self.mix.shape) != (S, S):
+                raise ValueError(f"{prefix}*: shapes do not match {S} streams")
 
 
 class _Layer:
-    def __init__(self, eng: "LayerListEngine", i: int, spec: LayerSpec):
+    def __init__(self, eng: "LayerListEngine", i: int, spec: LayerSpec, owner: Optional["_Layer"] = None):
         p = f"l{i}."
         if spec.type not in MIXERS:
             raise ValueError(f"layer {i}: unknown mixer type {spec.type!r}")
+        sandwich = eng.cfg.residual == "sandwich"
+        if owner is not None:
+            # the owner's weights on a cache / state of this layer's own
+            if spec.type != "attention" or sandwich:
+                raise ValueError(f"layer {i}: weights_of is only known for attention mixers of hyper-style models")
+            self.mixer = MIXERS[spec.type](eng, i, spec.mixer, "", share=owner.mixer)
+            self.ff = owner.ff
+            for n in ("norm1", "norm1b", "norm2", "norm2b", "hc1", "hc2"):
+                setattr(self, n, getattr(owner, n, None))
+            return
         self.mixer = MIXERS[spec.type](eng, i, spec.mixer, p + "mix.")
-        self.norm1, self.norm1b = eng.vector(p + "norm1"), eng.vector(p + "norm1b")
+        self.norm1 = eng.vector(p + "norm1")
+        self.norm1b = eng.vector(p + "norm1b") if sandwich else None
+        self.hc1 = self.hc2 = None
+        if not sandwich:
+            self.hc1 = _HyperWeights(eng, p + "hc1." if eng.cfg.hyper_weights else None)
         self.ff = None
         if spec.mlp is not None:
             kind = spec.mlp.get("kind", "dense")
             if kind not in FEED_FORWARDS:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
             self.ff = FEED_FORWARDS[kind](eng, i, spec.mlp, p + "mlp.")
-            self.norm2, self.norm2b = eng.vector(p + "norm2"), eng.vector(p + "norm2b")
+            self.norm2 = eng.vector(p + "norm2")
+            self.norm2b = eng.vector(p + "norm2b") if sandwich else None
+            if not sandwich:
+                self.hc2 = _HyperWeights(eng, p + "hc2." if eng.cfg.hyper_weights else None)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -306,7 +476,12 @@ class LayerListEngine:
             self.embed = self.weight("embed")
             if tuple(self.embed.shape) != (self.cfg.vocab, self.cfg.width):
                 raise ValueError(f"embed has shape {tuple(self.embed.shape)}")
-            self.layers = [_Layer(self, i, spec) for i, spec in enumerate(self.cfg.layers)]
+            self.layers: List[_Layer] = []
+            for i, spec in enumerate(self.cfg.layers):
+                owner = self.layers[spec.weights_of] if spec.weights_of is not None else None
+                if owner is not None and (spec.type, spec.mlp is None) != (self.cfg.layers[spec.weights_of].type, owner.ff is None):
+                    raise ValueError(f"layer {i}: its entry differs from layer {spec.weights_of}, whose weights it uses")
+                self.layers.append(_Layer(self, i, spec, owner))
             self.final_norm, self.head = self.vector("final.norm"), self.dense_weight(self.weight("head"))
         finally:
             self._st.close()
@@ -352,7 +527,9 @@ class LayerListEngine:
         if self.tc:       # activation slabs: one kept for a sublayer's input (several products read it), one for the rest
             n = L.xh_bytes(self._kmax, self.ncap)
             self._xh = {k: torch.zeros(n, dtype=torch.uint8, device=dev) for k in ("h", "tmp")}
-        self.x = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
+        if self.cfg.streams > L.HC_MAX_STREAMS:
+            raise ValueError(f"{self.cfg.streams} streams: the kernels keep at most {L.HC_MAX_STREAMS} copies of the residual stream")
+        self.x = torch.zeros(R, self.cfg.streams * self.cfg.width, dtype=torch.float32, device=dev)      # row = [streams][width]
         self.hn = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
         self.y = torch.zeros(R, self.cfg.width, dtype=torch.float32, device=dev)
         self.logits = torch.zeros(R, self.cfg.vocab, dtype=torch.float32, device=dev)
@@ -454,7 +631,7 @@ class LayerListEngine:
         return self._bufs[name][:self.max_rows * w].view(self.max_rows, w)
 
     def weight_bytes(self) -> int:
-        n = sum(l.mixer.weight_bytes() + (l.ff.weight_bytes() if l.ff else 0) for l in self.layers)
+        n = sum(l.mixer.weight_bytes() for l in self.layers) + sum(f.weight_bytes() for f in {id(l.ff): l.ff for l in self.layers if l.ff}.values())
         return n + self.head.nbytes()
 
     # ---- slots / pages ---------------------------------------------------------------------------
@@ -545,26 +722,58 @@ class LayerListEngine:
     def _launch_forward(self, M: int, n_logits: int):
         L, cfg, eps = self.L, self.cfg, self.cfg.norm_eps
         x, hn, y, W = self.x, self.hn, self.y, self.cfg.width
-        L.embed_rows(self.embed, self.tokens, x, M)
-        for l in self.layers:
-            L.rms_norm(x, hn, M, W, eps, w=l.norm1, plus_one=True)
-            self.begin_sublayer()
-            l.mixer.forward(hn, y, M)
-            L.rms_norm(y, x, M, W, eps, w=l.norm1b, plus_one=True, accumulate=True)
-            if l.ff is not None:
-                L.rms_norm(x, hn, M, W, eps, w=l.norm2, plus_one=True)
+        L.embed_rows(self.embed, self.tokens, x, M, cfg.embed_scale, cfg.streams)
+        if cfg.residual == "hyper":
+            self._launch_hyper_layers(M)
+            if n_logits:      # the copies summed, the model's norm, only the wanted rows
+                L.hyper_step(x, n_logits, cfg.streams, W, h=hn, norm_w=self.final_norm, eps=eps, rows=self.logit_rows)
+        else:
+            for l in self.layers:
+                L.rms_norm(x, hn, M, W, eps, w=l.norm1, plus_one=True)
                 self.begin_sublayer()
-                l.ff.forward(hn, y, M)
-                L.rms_norm(y, x, M, W, eps, w=l.norm2b, plus_one=True, accumulate=True)
-            if self.layer_probe is not None:
-                self.layer_probe.append(x[:M].clone())
+                l.mixer.forward(hn, y, M)
+                L.rms_norm(y, x, M, W, eps, w=l.norm1b, plus_one=True, accumulate=True)
+                if l.ff is not None:
+                    L.rms_norm(x, hn, M, W, eps, w=l.norm2, plus_one=True)
+                    self.begin_sublayer()
+                    l.ff.forward(hn, y, M)
+                    L.rms_norm(y, x, M, W, eps, w=l.norm2b, plus_one=True, accumulate=True)
+                if self.layer_probe is not None:
+                    self.layer_probe.append(x[:M].clone())
+            if n_logits:
+                L.rms_norm(x, hn, n_logits, W, eps, w=self.final_norm, plus_one=True, rows=self.logit_rows)
         if n_logits:
-            L.rms_norm(x, hn, n_logits, W, eps, w=self.final_norm, plus_one=True, rows=self.logit_rows)
             self.begin_sublayer()
             if cfg.logit_softcap > 0:
                 self.mm(self.head, hn, self.logits, n_logits, epi=L.DENSE_SOFTCAP, param=cfg.logit_softcap)
             else:
                 self.mm(self.head, hn, self.logits, n_logits)
+
+    def _launch_hyper_layers(self, M: int):
+        """Sublayer after sublayer on the copies of the residual stream.  The write of one sublayer's output and the read
+        (mix + norm) of the next sublayer's input are one launch; only a probe of the stream after every layer splits
+        them."""
+        L, cfg = self.L, self.cfg
+        x, hn, y, W, S, eps, mult = self.x, self.hn, self.y, cfg.width, cfg.streams, cfg.norm_eps, cfg.residual_mult
+        pending = None                                  # hyper weights of the sublayer whose output waits in y
+        for l in self.layers:
+            for sub, hc, norm in ((l.mixer, l.hc1, l.norm1), (l.ff, l.hc2, getattr(l, "norm2", None))):
+                if sub is None:
+                    continue
+                if pending is None:
+                    L.hyper_step(x, M, S, W, h=hn, w_in=hc.w_in, norm_w=norm, eps=eps)
+                else:
+                    L.hyper_step(x, M, S, W, y=y, mix=pending.mix, w_out=pending.w_out, mult=mult,
+                                 h=hn, w_in=hc.w_in, norm_w=norm, eps=eps)
+                self.begin_sublayer()
+                sub.forward(hn, y, M)
+                pending = hc
+            if self.layer_probe is not None:
+                L.hyper_step(x, M, S, W, y=y, mix=pending.mix, w_out=pending.w_out, mult=mult)
+                pending = None
+                self.layer_probe.append(x[:M].view(M, S, W).sum(1))
+        if pending is not None:
+            L.hyper_step(x, M, S, W, y=y, mix=pending.mix, w_out=pending.w_out, mult=mult)
 
     def _run(self, M: int, n_logits: int, greedy: bool):
         """Eagerly, or -- for decode-sized batches -- from a CUDA graph.  A shape's first step runs eagerly (it loads
@@ -650,10 +859,26 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
     def small(n, s=0.1):
         return (torch.randn(n, generator=g) * s).to(torch.bfloat16)
 
-    t = {"embed": (torch.randn(V, W, generator=g)).to(torch.bfloat16), "final.norm": small(W), "head": mat(V, W)}
+    sandwich = RESIDUAL_STYLES.get(config["architecture"], "sandwich") == "sandwich"
+    S = int(config.get("streams") or 0)
+    t = {"embed": (torch.randn(V, W, generator=g)).to(torch.bfloat16), "head": mat(V, W),
+         "final.norm": small(W) if sandwich else 1 + small(W)}
+
+    def hyper(prefix):
+        # read weights around 1 / S, write weights around 1, a mixing matrix near the identity with some cross-talk
+        t[prefix + "in"] = (1.0 / S + torch.randn(S, generator=g) * 0.1).to(torch.bfloat16)
+        t[prefix + "out"] = (1.0 + torch.randn(S, generator=g) * 0.2).to(torch.bfloat16)
+        t[prefix + "mix"] = (torch.eye(S) * 0.9 + torch.randn(S, S, generator=g) * 0.1).to(torch.bfloat16)
+
     for i, l in enumerate(config["layers"]):
         p, m = f"l{i}.", l["mixer"]
-        t[p + "norm1"], t[p + "norm1b"] = small(W), small(W)
+        if l.get("weights_of") is not None:
+            continue
+        t[p + "norm1"] = small(W) if sandwich else 1 + small(W)
+        if sandwich:
+            t[p + "norm1b"] = small(W)
+        elif S:
+            hyper(p + "hc1.")
         if l["type"] == "latent_attention":
             H, dn, dr, dv, qr, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
             t[p + "mix.dq"], t[p + "mix.dq.norm"] = mat(qr, W), 1 + small(qr)
@@ -671,11 +896,24 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             t[p + "mix.A_log"] = torch.log(torch.rand(H, generator=g) * 1.5 + 0.25).to(torch.bfloat16)
             t[p + "mix.D"], t[p + "mix.norm"] = 1 + small(H), 1 + small(inner)
             t[p + "mix.o"] = mat(W, inner)
+        elif l["type"] == "attention":
+            H, G, d = m["heads"], m["kv_heads"], m["dim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.o"] = mat(H * d, W, 2.0), mat(G * d, W, 2.0), mat(W, H * d)
         else:
             raise ValueError(f"layer {i}: unknown mixer type {l['type']!r}")
         if l.get("mlp"):
-            t[p + "norm2"], t[p + "norm2b"] = small(W), small(W)
-            t[p + "mlp.up"], t[p + "mlp.down"] = mat(l["mlp"]["ff"], W), mat(W, l["mlp"]["ff"])
+            t[p + "norm2"] = small(W) if sandwich else 1 + small(W)
+            if sandwich:
+                t[p + "norm2b"] = small(W)
+            elif S:
+                hyper(p + "hc2.")
+            if l["mlp"].get("kind", "dense") == "moe":
+                E, ff = l["mlp"]["router"]["experts"], l["mlp"]["expert"]["ff"]
+                t[p + "mlp.router"] = mat(E, W, 2.0)
+                for n in range(E):
+                    t[p + f"mlp.e{n}.up"], t[p + f"mlp.e{n}.down"] = mat(ff, W, 1.5), mat(W, ff)
+            else:
+                t[p + "mlp.up"], t[p + "mlp.down"] = mat(l["mlp"]["ff"], W), mat(W, l["mlp"]["ff"])
     return t
 
 
@@ -704,3 +942,21 @@ def example_config(width: int = 192, vocab: int = 320, blocks: int = 2, heads: i
                        "mixer": {"heads": heads, "vdim": 24, "state": 16, "groups": 2, "conv": 3, "norm_groups": 2}})
     return {"architecture": "Ribivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 25.0,
             "layers": layers}
+
+
+def example_config_sunesun(width: int = 160, vocab: int = 320, layers: int = 3, heads: int = 6, kv_heads: int = 3,
+                           window: int = 48, streams: int = 2) -> dict:
+    """A small Sunesun-shaped configuration: windowed attention (values = keys) with routed experts on `streams`
+    hyper-connected copies of the residual stream; the last layer runs the first layer's weights again."""
+    def layer(i):
+        l = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 32, "vdim": 32, "scale": 1.0 / math.sqrt(32.0), "softcap": 30.0,
+                       "mask": {"size": window},
+                       "rot": {"base": 10000.0, "dims": 24, "scaling": {"factor": 8.0, "original": 512, "fast": 16.0, "slow": 2.0}}},
+             "mlp": {"kind": "moe", "expert": {"ff": 64},
+                     "router": {"experts": 12, "top": 3, "groups": {"count": 3, "keep": 2}}}}
+        if i == layers - 1 and layers > 1:
+            l["weights_of"] = 0
+        return l
+    return {"architecture": "Sunesun", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+            "residual_mult": 0.5, "streams": streams, "layers": [layer(i) for i in range(layers)]}

@@ -19,6 +19,7 @@ def _layer_list(*args, **kw):
 # architecture name -> engine factory(model_path, rank=, world=, max_rows=, n_slots=, max_seq_len=, dtype=, ...)
 ARCHITECTURES: Dict[str, Callable] = {
     "Ribivik": _layer_list,        # mamba2 and latent_attention mixers in the order its configuration lists
+    "Sunesun": _layer_list,        # windowed attention (values = keys) + routed experts on hyper-connected residual streams
 }
 
 

@@ -11,9 +11,11 @@ import torch
 
 from . import lib
 from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
-                  DlEpilogue, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlNormArgs, check_layers, layers_lib)
+                  DlEpilogue, DlHyperArgs, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlMoeArgs,
+                  DlMoeSelectArgs, DlNormArgs, DlWindowAttnArgs, DlWindowKvArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
+HC_MAX_STREAMS = 8           # DL_HC_MAX_STREAMS of the hyper-connection kernel
 
 
 def _stream() -> int:
@@ -36,9 +38,10 @@ def sm_count() -> int:
     return int(layers_lib().dl_device_sm_count())
 
 
-def embed_rows(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, M: int):
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, M: int, scale: float = 1.0, copies: int = 1):
+    """x[m][c] = scale * table[tokens[m]] for each of `copies` copies of a row (x rows are [copies][dim])."""
     check_layers(layers_lib().dl_embed_rows(table.data_ptr(), _type(table), tokens.data_ptr(), x.data_ptr(), M,
-                                            table.shape[1], _stream()), "dl_embed_rows")
+                                            table.shape[1], scale, copies, _stream()), "dl_embed_rows")
     lib.count_launch()
 
 
@@ -138,9 +141,11 @@ def latent_kv_write(kv: torch.Tensor, M: int, norm_w: torch.Tensor, eps: float, 
 
 
 def rope_rows(x: torch.Tensor, M: int, n_heads: int, head_stride: int, offset: int, rope_dims: int, freqs: torch.Tensor,
-              pos: torch.Tensor):
+              pos: torch.Tensor, interleaved: bool = False, mag: float = 1.0):
+    """Rotary on dims [offset, offset + rope_dims) of every head, in place; pairs (i, i + dims/2) or, interleaved,
+    (2i, 2i + 1); cos and sin are multiplied by `mag`."""
     check_layers(layers_lib().dl_rope_rows(x.data_ptr(), x.stride(0), M, n_heads, head_stride, offset, rope_dims,
-                                           freqs.data_ptr(), pos.data_ptr(), _stream()), "dl_rope_rows")
+                                           freqs.data_ptr(), pos.data_ptr(), 1 if interleaved else 0, mag, _stream()), "dl_rope_rows")
     lib.count_launch()
 
 
@@ -220,6 +225,77 @@ def mamba_scan(batch: DlMambaBatch, n_seq: int, xbc: torch.Tensor, dt: torch.Ten
         return
     check_layers(layers_lib().dl_mamba_scan(batch, n_seq, a, _stream()), "dl_mamba_scan")
     lib.count_launch()
+
+
+# ---- hyper-connections ------------------------------------------------------------------------------------------------
+def hyper_step(x: torch.Tensor, M: int, streams: int, dim: int, y: Optional[torch.Tensor] = None,
+               mix: Optional[torch.Tensor] = None, w_out: Optional[torch.Tensor] = None, mult: float = 1.0,
+               h: Optional[torch.Tensor] = None, w_in: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+               eps: float = 0.0, rows: Optional[torch.Tensor] = None, u_out: Optional[torch.Tensor] = None):
+    """x [rows][streams * dim] f32.  With y: every copy is rewritten from the old ones (mix [from][to]) plus
+    mult * w_out[t] * y.  With h: h = rms_norm(sum_s w_in[s] x_s) * norm_w of the (new) copies.  One launch."""
+    a = DlHyperArgs()
+    a.x, a.ldx, a.streams, a.dim, a.M = x.data_ptr(), x.stride(0), streams, dim, M
+    a.y, a.ldy = _p(y), (y.stride(0) if y is not None else 0)
+    a.mix, a.w_out, a.mult = _p(mix), _p(w_out), mult
+    a.w_in, a.norm_w, a.eps, a.rows = _p(w_in), _p(norm_w), eps, _p(rows)
+    a.h, a.ldh, a.u_out = _p(h), (h.stride(0) if h is not None else 0), _p(u_out)
+    check_layers(layers_lib().dl_hyper_step(a, _stream()), "dl_hyper_step")
+    lib.count_launch()
+
+
+# ---- sliding-window attention whose values are its keys ---------------------------------------------------------------
+def window_kv_write(k: torch.Tensor, M: int, kv_heads: int, dim: int, rope_dims: int, freqs: torch.Tensor, rope_scale: float,
+                    pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
+    a = DlWindowKvArgs()
+    a.k, a.ld, a.kv_heads, a.dim, a.rope_dims = k.data_ptr(), k.stride(0), kv_heads, dim, rope_dims
+    a.freqs, a.rope_scale = freqs.data_ptr(), rope_scale
+    a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
+    a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
+    a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    check_layers(layers_lib().dl_window_kv_write(a, M, _stream()), "dl_window_kv_write")
+    lib.count_launch()
+
+
+def _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache):
+    a = DlWindowAttnArgs()
+    a.q, a.ldq, a.out, a.ldo = q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0)
+    a.heads, a.kv_heads, a.dim, a.rope_dims = heads, kv_heads, dim, rope_dims
+    a.scale, a.softcap, a.window = scale, softcap, window
+    a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
+    a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
+    a.cache, a.ctype = cache.data_ptr(), _type(cache)
+    return a
+
+
+def window_attention(q: torch.Tensor, out: torch.Tensor, M: int, heads: int, kv_heads: int, dim: int, rope_dims: int,
+                     scale: float, softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
+    """The per-row kernel (either cache type, f32 arithmetic)."""
+    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache)
+    check_layers(layers_lib().dl_window_attention(a, M, _stream()), "dl_window_attention")
+    lib.count_launch()
+
+
+# ---- routed experts ---------------------------------------------------------------------------------------------------
+def moe_select(z: torch.Tensor, M: int, experts: int, top: int, groups: int, keep: int, sel: torch.Tensor, wgt: torch.Tensor,
+               group_top: int = 2, renorm: bool = False):
+    a = DlMoeSelectArgs()
+    a.z, a.ldz, a.M, a.experts, a.top, a.groups, a.keep = z.data_ptr(), z.stride(0), M, experts, top, groups, keep
+    a.group_top, a.renorm, a.sel, a.wgt = group_top, 1 if renorm else 0, sel.data_ptr(), wgt.data_ptr()
+    check_layers(layers_lib().dl_moe_select(a, _stream()), "dl_moe_select")
+    lib.count_launch()
+
+
+def moe_rows(w_up: torch.Tensor, w_down: torch.Tensor, x: torch.Tensor, M: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
+             act: torch.Tensor, y: torch.Tensor, round_x: bool):
+    """w_up [experts][ff][width], w_down [experts][width][ff]; one product per (row, chosen expert) pair."""
+    a = DlMoeArgs()
+    a.w_up, a.w_down, a.wtype = w_up.data_ptr(), w_down.data_ptr(), _type(w_up)
+    a.width, a.ff, a.top, a.M, a.round_x = w_up.shape[2], w_up.shape[1], top, M, 1 if round_x else 0
+    a.x, a.ldx, a.sel, a.wgt = x.data_ptr(), x.stride(0), sel.data_ptr(), wgt.data_ptr()
+    a.act, a.y, a.ldy = act.data_ptr(), y.data_ptr(), y.stride(0)
+    check_layers(layers_lib().dl_moe_rows(a, _stream()), "dl_moe_rows")
+    lib.count_launch(2)
 
 
 _ARGMAX_SCRATCH = {}

@@ -210,7 +210,8 @@ def check(rc: int, what: str = ""):
         raise NativeLibraryError(f"{what} failed ({rc}): {msg}")
 
 
-# ---- libdllama_b200_layers.so: kernels of layer-list models (dense weights, latent attention, Mamba-2) --------------
+# ---- libdllama_b200_layers.so: kernels of layer-list models (dense weights, latent and windowed attention, Mamba-2,
+# ---- hyper-connections, routed experts)
 T_F32, T_BF16 = 0, 1
 DENSE_STORE, DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP = 0, 1, 2, 3
 
@@ -277,6 +278,46 @@ class DlMambaChunks(C.Structure):
                 ("state", C.c_void_p), ("decay", C.c_void_p), ("cum", C.c_void_p)]
 
 
+class DlHyperArgs(C.Structure):
+    """Mirror of ``DlHyperArgs``."""
+    _fields_ = [("x", C.c_void_p), ("ldx", C.c_longlong), ("streams", C.c_int), ("dim", C.c_int), ("M", C.c_int),
+                ("y", C.c_void_p), ("ldy", C.c_longlong), ("mix", C.c_void_p), ("w_out", C.c_void_p), ("mult", C.c_float),
+                ("w_in", C.c_void_p), ("norm_w", C.c_void_p), ("eps", C.c_float), ("rows", C.c_void_p),
+                ("h", C.c_void_p), ("ldh", C.c_longlong), ("u_out", C.c_void_p)]
+
+
+class DlWindowKvArgs(C.Structure):
+    """Mirror of ``DlWindowKvArgs``."""
+    _fields_ = [("k", C.c_void_p), ("ld", C.c_longlong), ("kv_heads", C.c_int), ("dim", C.c_int), ("rope_dims", C.c_int),
+                ("freqs", C.c_void_p), ("rope_scale", C.c_float),
+                ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
+                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
+
+
+class DlWindowAttnArgs(C.Structure):
+    """Mirror of ``DlWindowAttnArgs``."""
+    _fields_ = [("q", C.c_void_p), ("ldq", C.c_longlong), ("out", C.c_void_p), ("ldo", C.c_longlong),
+                ("heads", C.c_int), ("kv_heads", C.c_int), ("dim", C.c_int), ("rope_dims", C.c_int),
+                ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int),
+                ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
+                ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
+
+
+class DlMoeSelectArgs(C.Structure):
+    """Mirror of ``DlMoeSelectArgs``."""
+    _fields_ = [("z", C.c_void_p), ("ldz", C.c_longlong), ("M", C.c_int), ("experts", C.c_int), ("top", C.c_int),
+                ("groups", C.c_int), ("keep", C.c_int), ("group_top", C.c_int), ("renorm", C.c_int),
+                ("sel", C.c_void_p), ("wgt", C.c_void_p)]
+
+
+class DlMoeArgs(C.Structure):
+    """Mirror of ``DlMoeArgs``."""
+    _fields_ = [("w_up", C.c_void_p), ("w_down", C.c_void_p), ("wtype", C.c_int),
+                ("width", C.c_int), ("ff", C.c_int), ("top", C.c_int), ("M", C.c_int), ("round_x", C.c_int),
+                ("x", C.c_void_p), ("ldx", C.c_longlong), ("sel", C.c_void_p), ("wgt", C.c_void_p),
+                ("act", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong)]
+
+
 _layers = None
 
 
@@ -293,16 +334,21 @@ def layers_lib():
     L.dl_last_error.restype = C.c_char_p
     L.dl_device_sm_count.restype = i32
     L.dl_dense.argtypes = [C.POINTER(DlDenseArgs), vp]
-    L.dl_embed_rows.argtypes = [vp, i32, vp, vp, i32, i32, vp]
+    L.dl_embed_rows.argtypes = [vp, i32, vp, vp, i32, i32, C.c_float, i32, vp]
     L.dl_rms_norm.argtypes = [C.POINTER(DlNormArgs), vp]
     L.dl_latent_kv_write.argtypes = [C.POINTER(DlLatentKvArgs), i32, vp]
-    L.dl_rope_rows.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, vp]
+    L.dl_rope_rows.argtypes = [vp, i64, i32, i32, i32, i32, i32, vp, vp, i32, C.c_float, vp]
     L.dl_latent_attention.argtypes = [C.POINTER(DlLatentAttnArgs), i32, vp]
     L.dl_latent_attention_tc.argtypes = [C.POINTER(DlLatentAttnArgs), C.POINTER(DlLatentTiles), vp]
     L.dl_latent_attention_tc_supported.argtypes = [i32, i32, i32, i32, i32]
     L.dl_latent_attention_tc_supported.restype = i32
     L.dl_latent_tc_partial_floats.argtypes = [i32, i32, i32]
     L.dl_latent_tc_partial_floats.restype = i64
+    L.dl_hyper_step.argtypes = [C.POINTER(DlHyperArgs), vp]
+    L.dl_window_kv_write.argtypes = [C.POINTER(DlWindowKvArgs), i32, vp]
+    L.dl_window_attention.argtypes = [C.POINTER(DlWindowAttnArgs), i32, vp]
+    L.dl_moe_select.argtypes = [C.POINTER(DlMoeSelectArgs), vp]
+    L.dl_moe_rows.argtypes = [C.POINTER(DlMoeArgs), vp]
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
     L.dl_mamba_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), C.POINTER(DlMambaScanArgs), C.POINTER(DlMambaChunks), vp]
@@ -319,7 +365,7 @@ def layers_lib():
     L.dl_argmax_scratch_bytes.argtypes = [i32]
     for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention", "dl_latent_attention_tc",
                  "dl_mamba_conv", "dl_mamba_scan", "dl_mamba_scan_chunked", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
-                 "dl_gemm_wh_tc"):
+                 "dl_gemm_wh_tc", "dl_hyper_step", "dl_window_kv_write", "dl_window_attention", "dl_moe_select", "dl_moe_rows"):
         getattr(L, name).restype = i32
     _layers = L
     return L

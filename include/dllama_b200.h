@@ -307,8 +307,8 @@ int dl_peer_barrier(uint32_t* const* flags_on_peers /*host array*/, uint32_t* my
                     uint32_t epoch, void* stream);
 
 /* ==== layer-list models: dense bf16 / f32 weights, latent attention, Mamba-2 ===================
- * Built into libdllama_b200_layers.so (dense.cu, norms.cu, latent_attention.cu, mamba2.cu, plus the shared
- * prep.cu and sampler.cu).  Activations between kernels are f32; `wtype` / `ctype`: 0 = f32, 1 = bf16. */
+ * Built into libdllama_b200_layers.so (dense.cu, norms.cu, latent_attention.cu, mamba2.cu, hyper.cu, window_attention.cu,
+ * moe.cu, plus the shared prep.cu, sampler.cu and gemm_wh_tc.cu).  Activations between kernels are f32; `wtype` / `ctype`: 0 = f32, 1 = bf16. */
 
 /* Y[b][m][n] = epi( sum_k X[b][m][k] * W[b][n][k] ),  b < batch (element strides *_bs).  round_x: the activation
  * operand is rounded to bf16 on load (bf16 mode).  DL_DENSE_SIGMOID_MUL: aux[m][n] * sigmoid(.);
@@ -324,7 +324,9 @@ typedef struct {
     float param;
 } DlDenseArgs;
 int dl_dense(const DlDenseArgs* args /*host*/, void* stream);
-int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, void* stream);
+/* x[m][c][dim] = scale * table[tokens[m]] for c < copies */
+int dl_embed_rows(const void* table, int wtype, const int* tokens, float* x, int M, int dim, float scale, int copies,
+                  void* stream);
 /* Tensor-core path of the same product for bf16 weights and many rows: dl_gemm_wh_tc (flags bit 1 = bf16 operands) on
  * the pre-tiled images these two write.  Weights [N][K] row-major bf16 -> tiles of 128 rows x 128 K in the UMMA K-major
  * core-matrix image, [ceil(N/128)][ceil(K/128)][32 KB], zero-padded (dl_wh_bytes(N, round_up(K, 128)) bytes).
@@ -359,8 +361,10 @@ typedef struct {
     void* cache; int ctype;
 } DlLatentKvArgs;
 int dl_latent_kv_write(const DlLatentKvArgs* args /*host*/, int M, void* stream);
+/* rotary on dims [offset, offset + rope_dims) of every head of x, in place.  interleaved: dimension 2i pairs with 2i + 1
+ * (else i with i + rope_dims / 2); mag multiplies cos and sin (1: a pure rotation) */
 int dl_rope_rows(float* x, long long ld, int M, int n_heads, int head_stride, int offset, int rope_dims,
-                 const double* freqs, const int* pos, void* stream);
+                 const double* freqs, const int* pos, int interleaved, float mag, void* stream);
 
 /* attention of M rows over the paged latent cache.  q_lat[M][n_heads][rank]: queries already multiplied by the
  * key up-projection; q[M][ldq] holds each head's rotated part at q_head_stride * h + q_rot_offset.
@@ -421,6 +425,72 @@ typedef struct {
 int dl_mamba_scan_chunked_supported(int vdim, int state);
 int dl_mamba_scan_chunked(const DlMambaBatch* batch /*host*/, const DlMambaScanArgs* args /*host*/,
                           const DlMambaChunks* chunks /*host*/, void* stream);
+
+/* ---- hyper-connections: `streams` copies of the residual stream per row, x[m * ldx + s * dim + i] (hyper.cu) --------
+ * write (y != NULL):  x_t <- sum_s mix[s * streams + t] x_s + mult * w_out[t] * y[m]     for all t, from the old copies
+ * read  (h != NULL):  u = sum_s w_in[s] x_s (w_in NULL: ones);  h[m] = u / sqrt(mean(u^2) + eps) * norm_w (NULL: 1)
+ * Both in one launch: the write of one sublayer with the read of the next.  `rows` gathers source rows (read only).
+ * streams = 1, mix = w_out = {1}: the plain residual sum x += mult * y. */
+#define DL_HC_MAX_STREAMS 8
+typedef struct {
+    float* x; long long ldx;
+    int streams, dim, M;
+    const float* y; long long ldy;
+    const float* mix; const float* w_out; float mult;
+    const float* w_in; const float* norm_w; float eps;
+    const int* rows;
+    float* h; long long ldh;
+    float* u_out;                             /* optional: the mixed vector [M][dim] */
+} DlHyperArgs;
+int dl_hyper_step(const DlHyperArgs* args /*host*/, void* stream);
+
+/* ---- sliding-window grouped-query attention whose values are its keys (window_attention.cu) -------------------------
+ * Cache line per token and key/value head: [ rot(k)[0 : dim] | k[0 : rope_dims] ]; cache [page][kv_head][page_size][dim +
+ * rope_dims].  Rotary: interleaved pairs, angle pos * freqs[i] (f64 [rope_dims / 2]), cos and sin times rope_scale. */
+typedef struct {
+    const float* k; long long ld;             /* [M][kv_heads * dim] projected keys, unrotated */
+    int kv_heads, dim, rope_dims;
+    const double* freqs; float rope_scale;
+    const int* pos; const int* slot; const int* block_table;
+    int max_pages, page_size;
+    void* cache; int ctype;
+} DlWindowKvArgs;
+int dl_window_kv_write(const DlWindowKvArgs* args /*host*/, int M, void* stream);
+/* out[m][h] = sum_j softmax_j(cap(scale q[m][h] . key_j)) value_j over the positions j with 0 <= pos[m] - j < window
+ * (window 0: every j <= pos[m]); cap(s) = softcap tanh(s / softcap) (softcap 0: none); q already rotated. */
+typedef struct {
+    const float* q; long long ldq;            /* [M][heads * dim] */
+    float* out; long long ldo;                /* [M][heads * dim] */
+    int heads, kv_heads, dim, rope_dims;
+    float scale, softcap;
+    int window;
+    const int* pos; const int* slot; const int* block_table;
+    int max_pages, page_size;
+    const void* cache; int ctype;
+} DlWindowAttnArgs;
+int dl_window_attention(const DlWindowAttnArgs* args /*host*/, int M, void* stream);
+
+/* ---- routed experts (moe.cu) ---------------------------------------------------------------------------------------- */
+/* s = sigmoid(z); groups of experts/groups neighbours scored by the sum of their group_top largest s, the `keep` best
+ * groups stay; sel / wgt [M][top]: the `top` eligible experts with the largest s, in that order, and their s (divided
+ * by their sum if renorm). */
+typedef struct {
+    const float* z; long long ldz;
+    int M, experts, top, groups, keep, group_top, renorm;
+    int* sel; float* wgt;
+} DlMoeSelectArgs;
+int dl_moe_select(const DlMoeSelectArgs* args /*host*/, void* stream);
+/* y[m] = sum_k wgt[m][k] * W_down[e] relu(W_up[e] x[m])^2, e = sel[m][k]; w_up [experts][ff][width], w_down
+ * [experts][width][ff]; act: scratch [M * top][ff].  Weight-streaming form: one product per (row, expert) pair. */
+typedef struct {
+    const void* w_up; const void* w_down; int wtype;
+    int width, ff, top, M, round_x;
+    const float* x; long long ldx;
+    const int* sel; const float* wgt;
+    float* act;
+    float* y; long long ldy;
+} DlMoeArgs;
+int dl_moe_rows(const DlMoeArgs* args /*host*/, void* stream);
 
 #ifdef __cplusplus
 }
