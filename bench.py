@@ -51,6 +51,9 @@ def parse_args():
     ap.add_argument("--layered", default="", help="instead of the headline benchmark: prefill and decode throughput of the "
                     "layer-list design (Ribivik: Mamba-2 + latent attention, bf16) beside a Q40 Llama of equal width, "
                     "feed-forward size and depth, at these sizes (comma separated: w2048, w4096); prints one JSON line")
+    ap.add_argument("--layered-design", default="ribivik", choices=("ribivik", "sunesun"),
+                    help="--layered: which layer-list design runs beside the Llama arm (ribivik: Mamba-2 + latent attention; "
+                         "sunesun: windowed attention whose values are its keys + routed experts on hyper-connected streams)")
     ap.add_argument("--layered-layers", type=int, default=4, help="--layered: layers of both models")
     ap.add_argument("--layered-prompt", type=int, default=2048, help="--layered: prompt length (one batch)")
     return ap.parse_args()
@@ -425,6 +428,26 @@ def layered_config(sz: dict, n_layers: int, vocab: int) -> dict:
             "layers": layers}
 
 
+# Sunesun at the same widths: the routed experts' ACTIVE size (top x expert ff) equals the Llama arm's ff
+SUNESUN_SIZES = {
+    "w2048": dict(heads=16, kv_heads=8, experts=32, expert_ff=1024, top=8, groups=4, keep=2),
+    "w4096": dict(heads=32, kv_heads=8, experts=16, expert_ff=1792, top=8, groups=4, keep=3),
+}
+
+
+def sunesun_config(name: str, n_layers: int, vocab: int, window: int = 1024) -> dict:
+    import math
+    sz, ss = LAYERED_SIZES[name], SUNESUN_SIZES[name]
+    layer = {"type": "attention",
+             "mixer": {"heads": ss["heads"], "kv_heads": ss["kv_heads"], "dim": 128, "vdim": 128, "scale": 1.0 / math.sqrt(128.0),
+                       "softcap": 50.0, "mask": {"size": window},
+                       "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+             "mlp": {"kind": "moe", "expert": {"ff": ss["expert_ff"]},
+                     "router": {"experts": ss["experts"], "top": ss["top"], "groups": {"count": ss["groups"], "keep": ss["keep"]}}}}
+    return {"architecture": "Sunesun", "width": sz["width"], "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.5, "streams": 4, "layers": [dict(layer) for _ in range(n_layers)]}
+
+
 def _time_ms(fn, warmup: int, steps: int):
     import torch
     for _ in range(warmup):
@@ -491,9 +514,10 @@ def run_layered(args):
     rows = {}
     for name in [s for s in args.layered.split(",") if s]:
         sz = LAYERED_SIZES[name]
-        d = os.path.join(args.model_dir, f"dllama_b200_layered_{name}_l{nl}")
+        design = args.layered_design
+        d = os.path.join(args.model_dir, f"dllama_b200_{'layered' if design == 'ribivik' else design}_{name}_l{nl}")
         if not os.path.exists(os.path.join(d, "model.safetensors")):
-            write_random_model(d, layered_config(sz, nl, vocab), seed=1)
+            write_random_model(d, layered_config(sz, nl, vocab) if design == "ribivik" else sunesun_config(name, nl, vocab), seed=1)
         eng = registry.engine_for_dir(d, max_rows=max(T, users), n_slots=users, max_seq_len=ctx, dtype="bfloat16")
         r = _bench_engine(eng, vocab, T, users, args.warmup, args.steps)
         r["weight_gb"] = eng.weight_bytes() / 1e9
@@ -511,8 +535,8 @@ def run_layered(args):
         le.close()
         del le
         torch.cuda.empty_cache()
-        rows[name] = {"ribivik_bf16": r, "llama_q40": q}
-    print(json.dumps({"layered": rows, "layers": nl, "prompt": T, "users": users, "steps": args.steps, "warmup": args.warmup,
+        rows[name] = {f"{args.layered_design}_bf16": r, "llama_q40": q}
+    print(json.dumps({"layered": rows, "design": args.layered_design, "layers": nl, "prompt": T, "users": users, "steps": args.steps, "warmup": args.warmup,
                       "data": "synthetic", "clocks": sampler.stop()}), flush=True)
 
 

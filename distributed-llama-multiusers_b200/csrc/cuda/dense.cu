@@ -273,6 +273,24 @@ __global__ void __launch_bounds__(256) xh_from_rows_kernel(const float* __restri
     }
 }
 
+// the same image with a row gather: image row i < n_rows holds source row rows[i] (negative: a row of zeros) -- the rows of
+// a routed feed-forward sorted by expert
+__global__ void __launch_bounds__(256) xh_gather_rows_kernel(const float* __restrict__ x, long long ldx, int n_rows, int K, int ncap,
+                                                             uint8_t* __restrict__ xh, const int* __restrict__ rows) {
+    const int g = blockIdx.x, kt = blockIdx.y;
+    uint8_t* out = xh + ((size_t)kt * (ncap >> 3) + g) * 2048;
+    for (int i = threadIdx.x; i < 8 * 16; i += blockDim.x) {
+        const int r = i & 7, c = i >> 3;
+        const int k0 = kt * 128 + c * 8;
+        const int at = g * 8 + r;
+        const int m = at < n_rows ? rows[at] : -1;
+        __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn((m >= 0 && k0 + j < K) ? x[(size_t)m * ldx + k0 + j] : 0.f);
+        *reinterpret_cast<uint4*>(out + c * 128 + r * 16) = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
 extern "C" int dl_wh_from_dense(const void* w, int N, int K, long long ldw, uint8_t* wh, void* stream) {
     if (N < 1 || K < 1) { dl_set_error("dl_wh_from_dense: empty matrix"); return -1; }
     const int KT = (K + 127) / 128, RT = (N + 127) / 128;
@@ -286,5 +304,14 @@ extern "C" int dl_xh_from_rows(const float* x, long long ldx, int M, int K, int 
     dim3 grid((M + 7) / 8, (K + 127) / 128);
     xh_from_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, M, K, ncap, xh);
     LAYER_CHECK_LAUNCH("dl_xh_from_rows");
+    return 0;
+}
+
+// image row i < n_rows holds source row rows[i] of x (device map; negative: zeros)
+extern "C" int dl_xh_gather_rows(const float* x, long long ldx, const int* rows, int n_rows, int K, int ncap, uint8_t* xh, void* stream) {
+    if (n_rows < 1 || K < 1 || ncap % 8 != 0 || ncap < n_rows || rows == nullptr) { dl_set_error("dl_xh_gather_rows: bad n_rows=%d / ncap=%d", n_rows, ncap); return -1; }
+    dim3 grid((n_rows + 7) / 8, (K + 127) / 128);
+    xh_gather_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(x, ldx, n_rows, K, ncap, xh, rows);
+    LAYER_CHECK_LAUNCH("dl_xh_gather_rows");
     return 0;
 }

@@ -15,6 +15,10 @@
 // 128-wide k step and CTA instead of 96 KB), which is what keeps the L2 -> shared-memory feed (about 43 B/clk per SM)
 // below the tensor pipe's appetite.  gemm_wh_tc_kernel<1> is the single-CTA variant (odd row-tile counts).
 //
+// Grouped mode: the same kernel runs one product per group of rows against that group's own weights (the experts of a
+// routed feed-forward: rows sorted by expert, segment bounds in device memory), so all experts are ONE launch and the
+// host never learns how many rows an expert got.
+//
 // Persistent CTAs walk the tile list (activation tiles fastest, so the CTAs that run at the same time share one
 // weight panel in L2); each CTA owns 128 TMEM lanes x 2 accumulators of 256 columns, so the epilogue of tile i
 // (TMEM -> registers -> smem chunk -> the shared fused epilogues of epilogue.cuh) overlaps the MMAs of tile i+1.
@@ -38,6 +42,12 @@ struct WhArgs {
     int pf_dist, pf_mask;              // weight tiles are pulled into L2 pf_dist k-steps ahead by the CTAs whose activation tile index & pf_mask == 0
     int dbg;                           // timing experiments (results invalid): 1 = no epilogue work, 2 = no MMAs, 4 = no activation copies
     int bf16;                          // both operand images hold bf16 instead of fp16 (dense-weight models)
+    // grouped mode (routed experts): n_groups weight images wh_group_bytes apart; group g multiplies the activation rows
+    // [grp[2g], grp[2g] + grp[2g+1]) (device memory; first rows are multiples of 8) and writes those output rows.  The
+    // tile list covers m_tiles activation tiles per group; tiles beyond a group's rows are skipped by every role alike.
+    const int* grp;
+    int n_groups;
+    long long wh_group_bytes;
     unsigned long long* tr;
     DlEpilogue epi;
 };
@@ -103,6 +113,24 @@ DL_DEVINL void wt_wait_cluster(uint64_t* bar, uint32_t parity, unsigned long lon
     }
 }
 
+// tile t -> group, weight row pair, activation tile; false: the tile lies beyond its group's rows
+struct WtTile { int g, rp, mt, row0, rows; };
+DL_DEVINL bool wt_tile(const WhArgs& a, int t, WtTile& w) {
+    const int per_group = a.n_tiles / a.n_groups;
+    w.g = t / per_group;
+    const int tt = t - w.g * per_group;
+    w.rp = tt / a.m_tiles;
+    w.mt = tt - w.rp * a.m_tiles;
+    if (a.grp) {
+        w.row0 = a.grp[2 * w.g];
+        w.rows = a.grp[2 * w.g + 1];
+    } else {
+        w.row0 = 0;
+        w.rows = a.M;
+    }
+    return w.mt * WT_NT < w.rows;
+}
+
 template <int CG>
 __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_constant__ WhArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -125,7 +153,7 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
     uint32_t crank = 0;
     if (CG == 2) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(crank));
     const int cid = blockIdx.x / CG, ncl = gridDim.x / CG;
-    const int KT = a.KT, m_tiles = a.m_tiles;
+    const int KT = a.KT;
 
     if (tid == 0) {
         for (int s = 0; s < NS; s++) {
@@ -157,15 +185,18 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
             const size_t x_kt_stride = (size_t)(a.ncap >> 3) * XH_ROWGROUP_BYTES;
             uint32_t it = 0;
             for (int t = cid; t < a.n_tiles; t += ncl) {
-                const int rp = t / m_tiles, mt = t - rp * m_tiles;
+                WtTile w;
+                if (!wt_tile(a, t, w)) continue;
+                const int rp = w.rp, mt = w.mt;
                 const int rt = rp * CG + (int)crank;
-                const int mrow0 = mt * WT_NT + (int)crank * B_ROWS;
-                const int b_rows = max(0, min(B_ROWS, a.ncap - mrow0));
+                const int mrow0 = w.row0 + mt * WT_NT + (int)crank * B_ROWS;
+                const int row_cap = a.grp ? w.row0 + ((w.rows + 7) & ~7) : a.ncap;      // slabs hold 8 rows
+                const int b_rows = max(0, min(B_ROWS, row_cap - mrow0));
                 const uint8_t* src;
                 size_t stride;
                 uint32_t bytes;
                 if (lane < na) {
-                    src = a.wh + (size_t)rt * KT * WH_TILE_BYTES + lane * piece;
+                    src = a.wh + (size_t)w.g * (size_t)a.wh_group_bytes + (size_t)rt * KT * WH_TILE_BYTES + lane * piece;
                     stride = WH_TILE_BYTES;
                     bytes = piece;
                 } else {
@@ -175,13 +206,13 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
                     bytes = (a.dbg & 4) ? 0u : (uint32_t)max(0, min(prow, b_rows - r0)) * 256u;
                 }
                 const uint32_t total = WH_TILE_BYTES + ((a.dbg & 4) ? 0u : (uint32_t)b_rows * 256u);
-                const bool pf = lane < na && a.pf_dist > 0 && (mt & a.pf_mask) == 0;
+                const bool pf = lane < na && a.pf_dist > 0 && (mt & a.pf_mask) == 0 && a.n_groups == 1;
                 for (int kt = 0; kt < KT; kt++, it++) {
                     if (pf) {      // optional: pull the weight tile pf_dist k-steps ahead into L2 (measured: no gain, off by default)
                         int j = kt + a.pf_dist, tt = t;
                         while (j >= KT) { j -= KT; tt += ncl; }
                         if (tt < a.n_tiles) {
-                            const int rt2 = (tt / m_tiles) * CG + (int)crank;
+                            const int rt2 = (tt / a.m_tiles) * CG + (int)crank;
                             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.wh + ((size_t)rt2 * KT + j) * WH_TILE_BYTES + lane * piece),
                                          "r"(piece)
                                          : "memory");
@@ -200,7 +231,9 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
             const uint32_t idesc = umma_idesc_f16_f32(128 * CG, WT_NT) | (a.bf16 ? ((1u << 7) | (1u << 10)) : 0u);   // a_format = b_format = BF16
             const uint32_t desc_hi = (2048u >> 4) | (1u << 14);      // SBO 2048 B (8-row groups), descriptor version 1
             uint32_t it = 0, tcount = 0;
-            for (int t = cid; t < a.n_tiles; t += ncl, tcount++) {
+            for (int t = cid; t < a.n_tiles; t += ncl) {
+                WtTile w;
+                if (!wt_tile(a, t, w)) continue;
                 const uint32_t u = tcount & 1;
                 if (tcount >= 2) {      // the epilogue(s) of the tile that last used this accumulator are done with it
                     if (CG == 2) wt_wait_cluster(&acc_empty[u], ((tcount >> 1) & 1) ^ 1, t0);
@@ -229,12 +262,15 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
                     }
                     __syncwarp();
                 }
+                tcount++;
             }
         } else {
             // second CTA of a pair: tell the leader when this CTA's half of a stage has landed
             const uint32_t leader_pf = mapa_shared(smem_u32(peer_full), 0);
             uint32_t it = 0;
             for (int t = cid; t < a.n_tiles; t += ncl) {
+                WtTile w;
+                if (!wt_tile(a, t, w)) continue;
                 for (int kt = 0; kt < KT; kt++, it++) {
                     const uint32_t s = it % NS;
                     wt_wait(&full[s], (it / NS) & 1, t0);
@@ -252,11 +288,12 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
         uint32_t tcount = 0;
         const uint32_t leader_ae = (CG == 2) ? mapa_shared(smem_u32(acc_empty), 0) : 0u;
         bool first = true;
-        for (int t = cid; t < a.n_tiles; t += ncl, tcount++) {
-            const int rp = t / m_tiles, mt = t - rp * m_tiles;
-            const int rt = rp * CG + (int)crank;
-            const int m0 = mt * WT_NT;
-            const int Mt = min(WT_NT, a.M - m0);
+        for (int t = cid; t < a.n_tiles; t += ncl) {
+            WtTile w;
+            if (!wt_tile(a, t, w)) continue;
+            const int rt = w.rp * CG + (int)crank;
+            const int m0 = w.mt * WT_NT;
+            const int Mt = min(WT_NT, w.rows - m0);
             const uint32_t u = tcount & 1;
             wt_wait(&acc_full[u], (tcount >> 1) & 1, t0);
             tc_fence_after();
@@ -276,9 +313,10 @@ __global__ void __launch_bounds__(WT_THREADS, 1) gemm_wh_tc_kernel(const __grid_
                     if (CG == 2 && crank != 0) mbar_arrive_remote(leader_ae + u * 8);
                     else mbar_arrive(&acc_empty[u]);
                 }
-                if (!(a.dbg & 1)) epilogue_rows(a.epi, out_s, 128, 128, rt * 128, a.d_real, mc, m0 + ch * WT_EPI_CHUNK, etid, eg, 4);
+                if (!(a.dbg & 1)) epilogue_rows(a.epi, out_s, 128, 128, rt * 128, a.d_real, mc, w.row0 + m0 + ch * WT_EPI_CHUNK, etid, eg, 4);
                 asm volatile("bar.sync 1, 512;");
             }
+            tcount++;
         }
     }
     tc_fence_before();
@@ -346,8 +384,8 @@ extern "C" int dl_q40t_to_wh(const uint8_t* q40t, int d, int n, uint8_t* wh, voi
 
 // force_cg: bit 0: 0 = pairs when the row-tile count is even, 1 = single CTAs (for tests and comparisons);
 // bit 1: the images hold bf16 (written by dl_wh_from_dense / dl_xh_from_rows) instead of fp16
-extern "C" int dl_gemm_wh_tc(const uint8_t* wh, int d, int n, const uint8_t* xh, int ncap, int M, const DlEpilogue* epi,
-                             int force_cg, int pdl, void* stream) {
+static int gemm_wh_launch(const uint8_t* wh, int d, int n, const uint8_t* xh, int ncap, int M, const DlEpilogue* epi,
+                          int force_cg, int pdl, const int* grp, int n_groups, long long wh_group_bytes, void* stream) {
     if (n % 128 != 0) { dl_set_error("dl_gemm_wh_tc: n=%d not a multiple of 128", n); return -1; }
     if (M < 1 || ncap % 8 != 0 || ncap < M) { dl_set_error("dl_gemm_wh_tc: bad M=%d / ncap=%d", M, ncap); return -1; }
     if (epi->kind == DL_EPI_SILU_MUL && d % 64 != 0) { dl_set_error("dl_gemm_wh_tc: silu epilogue needs d%%64==0"); return -1; }
@@ -358,7 +396,8 @@ extern "C" int dl_gemm_wh_tc(const uint8_t* wh, int d, int n, const uint8_t* xh,
     a.m_tiles = (M + WT_NT - 1) / WT_NT;
     const int cg = ((force_cg & 1) || (a.row_tiles & 1)) ? 1 : 2;
     a.bf16 = (force_cg & 2) ? 1 : 0;
-    a.n_tiles = (a.row_tiles / cg) * a.m_tiles;
+    a.grp = grp; a.n_groups = n_groups; a.wh_group_bytes = wh_group_bytes;
+    a.n_tiles = n_groups * (a.row_tiles / cg) * a.m_tiles;
     const int n_sms = dl_device_sm_count();
     int grid = (n_sms / cg) * cg;
     if (grid > a.n_tiles * cg) grid = a.n_tiles * cg;
@@ -401,4 +440,20 @@ extern "C" int dl_gemm_wh_tc(const uint8_t* wh, int d, int n, const uint8_t* xh,
     cudaError_t e = (cg == 2) ? cudaLaunchKernelEx(&cfg, gemm_wh_tc_kernel<2>, a) : cudaLaunchKernelEx(&cfg, gemm_wh_tc_kernel<1>, a);
     if (e != cudaSuccess) { dl_set_error("gemm wh launch: %s", cudaGetErrorString(e)); return -(int)e; }
     return 0;
+}
+
+extern "C" int dl_gemm_wh_tc(const uint8_t* wh, int d, int n, const uint8_t* xh, int ncap, int M, const DlEpilogue* epi,
+                             int force_cg, int pdl, void* stream) {
+    return gemm_wh_launch(wh, d, n, xh, ncap, M, epi, force_cg, pdl, nullptr, 1, 0, stream);
+}
+
+// One product per group: group g < n_groups multiplies activation rows [grp[2g], grp[2g] + grp[2g+1]) of xh (grp in DEVICE
+// memory, first rows multiples of 8, every group at most max_group_rows rows) with the weight image at
+// wh + g * wh_group_bytes, and writes those rows of the output.
+extern "C" int dl_gemm_wh_tc_grouped(const uint8_t* wh, long long wh_group_bytes, int n_groups, const int* grp, int d, int n,
+                                     const uint8_t* xh, int ncap, int max_group_rows, const DlEpilogue* epi, int force_cg,
+                                     void* stream) {
+    if (n_groups < 1 || grp == nullptr || max_group_rows < 1) { dl_set_error("dl_gemm_wh_tc_grouped: bad groups"); return -1; }
+    if (max_group_rows > ncap) max_group_rows = ncap;
+    return gemm_wh_launch(wh, d, n, xh, ncap, max_group_rows, epi, force_cg, 0, grp, n_groups, wh_group_bytes, stream);
 }

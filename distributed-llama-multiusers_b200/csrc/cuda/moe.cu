@@ -184,3 +184,83 @@ extern "C" int dl_moe_rows(const DlMoeArgs* args, void* stream) {
     LAYER_CHECK_LAUNCH("dl_moe_rows");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// grouped form: sort the (row, expert) pairs by expert -- stable, so nothing depends on timing -- into segments whose
+// first rows are multiples of 8 (the row granularity of the GEMM's activation image)
+//   cnt[e]              pairs of expert e                                  (moe_count_kernel; cnt zeroed before)
+//   grp[e] = {first, n} segment of expert e among the sorted rows
+//   slot_row[i]         the batch row whose input sorted row i holds, -1 for padding rows (up to `cap`)
+//   pair_pos[m*top+k]   the sorted row of pair (m, k)
+// ------------------------------------------------------------------------------------------------
+__global__ void moe_count_kernel(const int* __restrict__ sel, int n_pairs, int* __restrict__ cnt) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_pairs) atomicAdd(cnt + sel[i], 1);
+}
+
+#define MP_THREADS 1024
+
+__global__ void __launch_bounds__(MP_THREADS) moe_place_kernel(DlMoePlanArgs a) {
+    __shared__ int wc[MP_THREADS / 32];
+    const int e = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = MP_THREADS / 32;
+    const int n_pairs = a.M * a.top;
+    int first = 0;
+    for (int i = 0; i < e; ++i) first += (a.cnt[i] + 7) & ~7;
+    const int mine = a.cnt[e];
+    // every warp takes a contiguous run of pairs (a multiple of 32): count, prefix over the warps, place
+    const int seg = ((n_pairs + nw - 1) / nw + 31) & ~31;
+    const int lo = warp * seg, hi = min(n_pairs, lo + seg);
+    int c = 0;
+    for (int b = lo; b < hi; b += 32) {
+        const bool hit = b + lane < hi && a.sel[b + lane] == e;
+        c += __popc(__ballot_sync(0xffffffffu, hit));
+    }
+    if (lane == 0) wc[warp] = c;
+    __syncthreads();
+    int at = first;
+    for (int w = 0; w < warp; ++w) at += wc[w];
+    for (int b = lo; b < hi; b += 32) {
+        const bool hit = b + lane < hi && a.sel[b + lane] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+            const int p = at + __popc(bal & ((1u << lane) - 1u));
+            a.slot_row[p] = (b + lane) / a.top;
+            a.pair_pos[b + lane] = p;
+        }
+        at += __popc(bal);
+    }
+    const int end = first + ((mine + 7) & ~7);
+    for (int p = first + mine + threadIdx.x; p < (e == a.experts - 1 ? a.cap : end); p += MP_THREADS) a.slot_row[p] = -1;
+    if (threadIdx.x == 0) { a.grp[2 * e] = first; a.grp[2 * e + 1] = mine; }
+}
+
+extern "C" int dl_moe_plan(const DlMoePlanArgs* args, void* stream) {
+    const DlMoePlanArgs& a = *args;
+    if (a.M < 1 || a.top < 1 || a.experts < 1 || a.cap < a.M * a.top + 7 * a.experts) { dl_set_error("dl_moe_plan: bad sizes"); return -1; }
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(a.cnt, 0, sizeof(int) * a.experts, st);
+    if (e != cudaSuccess) { dl_set_error("dl_moe_plan: %s", cudaGetErrorString(e)); return -(int)e; }
+    const int n_pairs = a.M * a.top;
+    moe_count_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(a.sel, n_pairs, a.cnt);
+    moe_place_kernel<<<a.experts, MP_THREADS, 0, st>>>(a);
+    LAYER_CHECK_LAUNCH("dl_moe_plan");
+    return 0;
+}
+
+// y[m] = sum_k wgt[m][k] * yp[pair_pos[m][k]], in the order the experts were chosen
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ yp, long long ldp, const int* __restrict__ pair_pos,
+                                                          const float* __restrict__ wgt, int top, int width, float* __restrict__ y, long long ldy) {
+    const int m = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(wgt[m * top + k], yp[(size_t)pair_pos[m * top + k] * ldp + c], acc);
+        y[(size_t)m * ldy + c] = acc;
+    }
+}
+
+extern "C" int dl_moe_combine(const float* yp, long long ldp, const int* pair_pos, const float* wgt, int M, int top, int width,
+                              float* y, long long ldy, void* stream) {
+    moe_combine_kernel<<<M, 256, 0, (cudaStream_t)stream>>>(yp, ldp, pair_pos, wgt, top, width, y, ldy);
+    LAYER_CHECK_LAUNCH("dl_moe_combine");
+    return 0;
+}

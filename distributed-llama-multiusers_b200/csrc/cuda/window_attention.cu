@@ -144,3 +144,203 @@ extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* st
     LAYER_CHECK_LAUNCH("dl_window_attention");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Tensor-core kernel (bf16 cache): a CTA owns a tile of up to `rq` consecutive positions of one sequence and one
+// key/value head g; the heads/kv_heads query heads of the group read the same cache lines, so (position, head) pairs
+// stack on the M dimension of the MMA: 4 warps x 16 stacked rows.  The CTA walks the pages that the tile's windows
+// touch; per page (32 tokens), per warp:
+//     S[16 x 32]  = Q[16 x D] . K[32 x D]^T        Q fragments stay in registers (bf16), K by ldmatrix
+//     scale, soft cap, window mask, online softmax in f32 (two rows per thread, reduced over the quad)
+//     O[16 x D]  += P[16 x 32] . V[32 x D]         P from the score registers, V by ldmatrix.trans from the SAME staged
+//                                                  line: value column c sits at D + c (c < rope_dims) or at c
+// mma.sync m16n8k16 bf16, f32 accumulators.  Pages arrive by cp.async into two buffers (page k + 1 in flight while
+// page k is multiplied).  tile_rows[n_tiles][rq]: row indices of the batch, -1 where a tile has fewer rows.
+// ------------------------------------------------------------------------------------------------
+#define WM_ROWS 64
+
+__host__ __device__ __forceinline__ int wm_line_stride(int LD) {      // bf16 elements; rows 16 B apart modulo 128 B
+    int s = (LD + 7) / 8 * 8 + 8;
+    if ((s * 2) % 128 == 0) s += 8;
+    return s;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq) {
+    constexpr int D = 16 * DK, NV = D / 8;
+    extern __shared__ __align__(16) uint8_t smraw[];
+    __shared__ int s_row[WM_ROWS];
+    const int RD = a.rope_dims, LD = D + RD, LDS = wm_line_stride(LD);
+    __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][WA_PAGE][LDS]
+    const int tile = blockIdx.x, g = blockIdx.y, rep = a.heads / a.kv_heads;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    if (threadIdx.x < rq) s_row[threadIdx.x] = tile_rows[(size_t)tile * rq + threadIdx.x];
+    __syncthreads();
+    int n_rows = 0;
+    while (n_rows < rq && s_row[n_rows] >= 0) ++n_rows;
+    if (n_rows == 0) return;
+    const int p_first = a.pos[s_row[0]], p_last = p_first + n_rows - 1, slot = a.slot[s_row[0]];
+    const int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
+    const int pg_lo = lo / WA_PAGE, pg_hi = p_last / WA_PAGE;
+    const bool active = warp * 16 < n_rows * rep;
+
+    // this thread's two stacked rows: s = position-in-tile * rep + head-in-group
+    const int s0 = warp * 16 + gid, s1 = s0 + 8;
+    const int r0 = s0 / rep, r1 = s1 / rep;
+    const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
+    const int pos0 = p_first + r0, pos1 = p_first + r1;
+    const size_t q_off0 = ok0 ? (size_t)s_row[r0] * a.ldq + (size_t)(g * rep + s0 % rep) * D : 0;
+    const size_t q_off1 = ok1 ? (size_t)s_row[r1] * a.ldq + (size_t)(g * rep + s1 % rep) * D : 0;
+    uint32_t qf[DK][4];
+#pragma unroll
+    for (int kk = 0; kk < DK; ++kk) {
+        const int c = kk * 16 + tig * 2;
+        float2 u0 = make_float2(0.f, 0.f), u1 = u0, v0 = u0, v1 = u0;
+        if (ok0) { u0 = *reinterpret_cast<const float2*>(a.q + q_off0 + c); v0 = *reinterpret_cast<const float2*>(a.q + q_off0 + c + 8); }
+        if (ok1) { u1 = *reinterpret_cast<const float2*>(a.q + q_off1 + c); v1 = *reinterpret_cast<const float2*>(a.q + q_off1 + c + 8); }
+        qf[kk][0] = pack_bf16(u0.x, u0.y);
+        qf[kk][1] = pack_bf16(u1.x, u1.y);
+        qf[kk][2] = pack_bf16(v0.x, v0.y);
+        qf[kk][3] = pack_bf16(v1.x, v1.y);
+    }
+    float o[NV][4];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) { o[v][0] = o[v][1] = o[v][2] = o[v][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int chunks_per_line = LD / 8, n_chunks = WA_PAGE * chunks_per_line;
+    auto issue = [&](int pg, int buf) {
+        const int page = a.block_table[(size_t)slot * a.max_pages + pg];
+        const __nv_bfloat16* src = (const __nv_bfloat16*)a.cache + ((size_t)page * a.kv_heads + g) * WA_PAGE * LD;
+        __nv_bfloat16* dst = kv_s + (size_t)buf * WA_PAGE * LDS;
+        for (int c = threadIdx.x; c < n_chunks; c += 128) {
+            const int j = c / chunks_per_line, part = c - j * chunks_per_line;
+            cp_async16(dst + (size_t)j * LDS + part * 8, src + (size_t)j * LD + part * 8);
+        }
+    };
+    issue(pg_lo, 0);
+    const int mat = lane >> 3, rr = lane & 7;
+    for (int pg = pg_lo; pg <= pg_hi; ++pg) {
+        const int buf = (pg - pg_lo) & 1;
+        cp_async_wait_all();
+        __syncthreads();                      // page pg has landed; everyone is done with the other buffer
+        if (pg < pg_hi) issue(pg + 1, buf ^ 1);
+        if (!active) continue;
+        const __nv_bfloat16* kv = kv_s + (size_t)buf * WA_PAGE * LDS;
+        float sc[4][4];
+#pragma unroll
+        for (int n = 0; n < 4; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < DK; ++kk) {
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kv + (size_t)(np * 16 + (mat >> 1) * 8 + rr) * LDS + kk * 16 + (mat & 1) * 8);
+                mma_bf16(sc[2 * np], qf[kk], b[0], b[1]);
+                mma_bf16(sc[2 * np + 1], qf[kk], b[2], b[3]);
+            }
+        }
+        // scale, soft cap, mask
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = pg * WA_PAGE + n * 8 + tig * 2 + (e & 1);
+                const int pr = (e < 2) ? pos0 : pos1;
+                const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window);
+                float s = sc[n][e] * a.scale;
+                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+                s = vis ? s : -INFINITY;
+                sc[n][e] = s;
+                if (e < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float al0 = (m0 == -INFINITY) ? 0.f : expf(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : expf(m1 - mn1);
+        const float ref0 = (mn0 == -INFINITY) ? 0.f : mn0, ref1 = (mn1 == -INFINITY) ? 0.f : mn1;      // a row that sees nothing yet: every p = 0
+        m0 = mn0; m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            sc[n][0] = expf(sc[n][0] - ref0); sc[n][1] = expf(sc[n][1] - ref0);
+            sc[n][2] = expf(sc[n][2] - ref1); sc[n][3] = expf(sc[n][3] - ref1);
+            ps0 += sc[n][0] + sc[n][1];
+            ps1 += sc[n][2] + sc[n][3];
+        }
+        l0 = l0 * al0 + ps0;
+        l1 = l1 * al1 + ps1;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) { o[v][0] *= al0; o[v][1] *= al0; o[v][2] *= al1; o[v][3] *= al1; }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+            pa[1] = pack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
+            pa[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+            pa[3] = pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+            for (int vp = 0; vp < NV / 2; ++vp) {
+                const int vt = 2 * vp + (mat >> 1);
+                const int col = vt * 8 < RD ? D + vt * 8 : vt * 8;            // the value's first entries sit behind the key
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, kv + (size_t)(ks * 16 + (mat & 1) * 8 + rr) * LDS + col);
+                mma_bf16(o[2 * vp], pa, b[0], b[1]);
+                mma_bf16(o[2 * vp + 1], pa, b[2], b[3]);
+            }
+        }
+    }
+    if (!active) return;
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (ok0) {
+        float* dst = a.out + (size_t)s_row[r0] * a.ldo + (size_t)(g * rep + s0 % rep) * D;
+        const float inv = 1.f / l0;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][0] * inv, o[v][1] * inv);
+    }
+    if (ok1) {
+        float* dst = a.out + (size_t)s_row[r1] * a.ldo + (size_t)(g * rep + s1 % rep) * D;
+        const float inv = 1.f / l1;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][2] * inv, o[v][3] * inv);
+    }
+}
+
+// rows of one sequence per tile: as many positions as fit 64 stacked (position, head) pairs
+extern "C" int dl_window_tc_rows(int heads, int kv_heads) {
+    if (heads < 1 || kv_heads < 1 || heads % kv_heads) return 0;
+    const int rep = heads / kv_heads;
+    return rep > WM_ROWS ? 0 : WM_ROWS / rep;
+}
+
+// 0 if the tensor-core kernel takes these sizes
+extern "C" int dl_window_attention_tc_supported(int heads, int kv_heads, int dim, int rope_dims, int ctype) {
+    if (ctype != DL_T_BF16 || dl_window_tc_rows(heads, kv_heads) == 0) return -1;
+    if (dim % 16 != 0 || dim > 128 || dim / 16 == 5 || dim / 16 == 7 || rope_dims % 8 != 0 || rope_dims > dim) return -1;
+    return 0;
+}
+
+extern "C" int dl_window_attention_tc(const DlWindowAttnArgs* args, const int* tile_rows, int n_tiles, int rq, void* stream) {
+    const DlWindowAttnArgs& a = *args;
+    if (window_args_ok(a, "dl_window_attention_tc")) return -1;
+    if (dl_window_attention_tc_supported(a.heads, a.kv_heads, a.dim, a.rope_dims, a.ctype) != 0 || rq < 1 || rq > dl_window_tc_rows(a.heads, a.kv_heads) ||
+        (a.ldq & 1) || (a.ldo & 1)) {
+        dl_set_error("dl_window_attention_tc: sizes not supported (heads %d / %d, dim %d, rotary %d, rq %d)", a.heads, a.kv_heads, a.dim, a.rope_dims, rq);
+        return -1;
+    }
+    if (n_tiles < 1) return 0;
+    const size_t smem = (size_t)2 * WA_PAGE * wm_line_stride(a.dim + a.rope_dims) * sizeof(__nv_bfloat16);
+    dim3 grid(n_tiles, a.kv_heads);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (a.dim / 16) {
+#define WM_CASE(DK_) case DK_: window_attention_mma_kernel<DK_><<<grid, 128, smem, st>>>(a, tile_rows, rq); break;
+        WM_CASE(1) WM_CASE(2) WM_CASE(3) WM_CASE(4) WM_CASE(6) WM_CASE(8)
+#undef WM_CASE
+        default: dl_set_error("dl_window_attention_tc: dim %d", a.dim); return -1;
+    }
+    LAYER_CHECK_LAUNCH("dl_window_attention_tc");
+    return 0;
+}

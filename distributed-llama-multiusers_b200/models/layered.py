@@ -327,6 +327,12 @@ class WindowAttentionMixer:
         self.owns_weights = share is None
         self.line = self.dim + self.rope_dims
         self.cache = torch.zeros(eng.n_pages, self.G, PAGE, self.line, dtype=eng.wdtype, device=eng.device)
+        # bf16 caches of sizes the tensor-core kernel takes: tiles of tc_rq consecutive rows of a sequence (0: per-row kernel)
+        L = eng.L
+        self.tc_rq = 0
+        if eng.round_x and os.environ.get("DLLAMA_LAYERS_ATTN_TC", "1") != "0" and \
+                L.window_tc_supported(self.H, self.G, self.dim, self.rope_dims, eng.wdtype):
+            self.tc_rq = L.window_tc_rows(self.H, self.G)
 
     def scratch(self) -> Dict[str, int]:
         return {"qk": (self.H + self.G) * self.dim, "o": self.H * self.dim}
@@ -345,8 +351,13 @@ class WindowAttentionMixer:
         if rd:
             L.rope_rows(qk, M, H, d, 0, rd, self.freqs, e.pos, interleaved=True, mag=self.rope_mag)
         L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache)
-        L.window_attention(qk, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
-                           self.cache)
+        if self.tc_rq:
+            tile_rows, n_tiles = e.window_tiles(self.tc_rq)
+            L.window_attention_tc(qk, o, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
+                                  self.cache, tile_rows, n_tiles, self.tc_rq)
+        else:
+            L.window_attention(qk, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
+                               self.cache)
         e.mm(self.w_o, o, y, M)
 
 
@@ -369,7 +380,9 @@ class RoutedExperts:
         self.w_down = torch.stack([eng.weight(f"{prefix}e{n}.down") for n in range(self.E)]).contiguous()    # [E][W][ff]
         if tuple(self.w_up.shape) != (self.E, self.ff, eng.cfg.width) or tuple(self.w_down.shape) != (self.E, eng.cfg.width, self.ff):
             raise ValueError(f"layer {index}: expert weights have shapes {tuple(self.w_up.shape)} / {tuple(self.w_down.shape)}")
-        eng._kmax = max(eng._kmax, self.ff, eng.cfg.width)
+        # bf16 mode: batches of TC_MIN_ROWS rows and more sort their (row, expert) pairs by expert and run all experts as
+        # one grouped tensor-core GEMM per projection; fewer rows stream the chosen experts' weights pair by pair
+        self.grouped = eng.L.MoeGrouped(self.w_up, self.w_down, self.top, eng.max_rows) if eng.tc else None
 
     def scratch(self) -> Dict[str, int]:
         return {"router_z": self.E, "moe_act": self.top * self.ff, "moe_sel": self.top, "moe_wgt": self.top}
@@ -383,7 +396,10 @@ class RoutedExperts:
         sel, wgt = e.buf("moe_sel", self.top).view(torch.int32), e.buf("moe_wgt", self.top)
         e.mm(self.router, h, z, M, src="h")
         L.moe_select(z, M, self.E, self.top, self.groups, self.keep, sel, wgt)
-        L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x)
+        if self.grouped is not None and M >= TC_MIN_ROWS:
+            self.grouped.run(h, M, sel, wgt, y)
+        else:
+            L.moe_rows(self.w_up, self.w_down, h, M, self.top, sel, wgt, act, y, e.round_x)
 
 
 MIXERS = {"latent_attention": LatentAttentionMixer, "mamba2": Mamba2Mixer, "attention": WindowAttentionMixer}
@@ -541,6 +557,12 @@ class LayerListEngine:
         self._tiles_off = 6 * R + 3 * S + 1                  # then tile_rows [n_tiles][rq] of the attention kernel
         self._chunks_off = self._tiles_off + R + 16 * S      # then chunk_seq | chunk_off [max_chunks] of the chunked scan
         self._desc_len = self._chunks_off + 2 * self._max_chunks
+        # then, per tile height rq of the windowed-attention layers, tile_rows [tiles][rq] of their tensor-core kernel
+        self._wtile_off: Dict[int, int] = {}
+        self._wtile_n: Dict[int, int] = {}
+        for rq in sorted({mx.tc_rq for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq}):
+            self._wtile_off[rq] = self._desc_len
+            self._desc_len += ((R + rq - 1) // rq + S) * rq
         self.tile_rows = None
         self.h_desc = torch.zeros(self._desc_len, dtype=torch.int32).pin_memory()
         self.desc = torch.zeros(self._desc_len, dtype=torch.int32, device=dev)
@@ -622,6 +644,11 @@ class LayerListEngine:
             return None
         return (self.tile_rows, self._n_tiles, self.attn_rq, self._n_splits, self._attn_partial)
 
+    def window_tiles(self, rq: int):
+        """(tile_rows on the device, tiles) of this batch for windowed-attention layers with tiles of rq rows."""
+        o = self._wtile_off[rq]
+        return self.desc[o:], self._wtile_n[rq]
+
     def begin_sublayer(self):
         self._xh_h_ready = False
 
@@ -698,6 +725,15 @@ class LayerListEngine:
                 pages = max(pages, (int(self._slot_len[s]) + PAGE - 1) // PAGE)
             self._n_tiles = nt
             self._n_splits = 1 if nt >= self.n_sms else max(1, min(32, (2 * self.n_sms) // nt, pages // 2))
+        for rq, wo in self._wtile_off.items():       # tiles of up to rq rows of one sequence at consecutive positions
+            nt = 0
+            for rows in by_slot.values():
+                for i in range(0, len(rows), rq):
+                    part = rows[i:i + rq]
+                    hd[wo + nt * rq:wo + nt * rq + len(part)] = part
+                    hd[wo + nt * rq + len(part):wo + (nt + 1) * rq] = -1
+                    nt += 1
+            self._wtile_n[rq] = nt
         self._n_chunks = 0
         if self._chunk_scratch is not None and max(len(r) for r in by_slot.values()) >= CHUNKED_SCAN_MIN_ROWS:
             co, nc, ch = self._chunks_off, 0, self.L.MAMBA_CHUNK
@@ -780,7 +816,7 @@ class LayerListEngine:
         modules and sets kernel attributes), its second is captured (capturing executes nothing: the recurrent state
         advances once per step) and replayed from then on."""
         from ..ops import lib as _lib
-        key = (M, self.n_seq, n_logits, self._n_tiles, self._n_splits, greedy)
+        key = (M, self.n_seq, n_logits, self._n_tiles, self._n_splits, greedy, tuple(self._wtile_n.values()))
         if not self.use_graphs or M > GRAPH_MAX_ROWS or self.layer_probe is not None:
             return self._launch_step(M, n_logits, greedy)
         g = self._graphs.get(key)

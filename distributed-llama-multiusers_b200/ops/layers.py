@@ -12,7 +12,7 @@ import torch
 from . import lib
 from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EPI_DENSE, T_BF16, T_F32, DlDenseArgs,  # noqa: F401
                   DlEpilogue, DlHyperArgs, DlLatentAttnArgs, DlLatentKvArgs, DlLatentTiles, DlMambaBatch, DlMambaChunks, DlMambaScanArgs, DlMoeArgs,
-                  DlMoeSelectArgs, DlNormArgs, DlWindowAttnArgs, DlWindowKvArgs, check_layers, layers_lib)
+                  DlMoePlanArgs, DlMoeSelectArgs, DlNormArgs, DlWindowAttnArgs, DlWindowKvArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
 HC_MAX_STREAMS = 8           # DL_HC_MAX_STREAMS of the hyper-connection kernel
@@ -276,6 +276,35 @@ def window_attention(q: torch.Tensor, out: torch.Tensor, M: int, heads: int, kv_
     lib.count_launch()
 
 
+def window_tc_rows(heads: int, kv_heads: int) -> int:
+    """Rows of one sequence per tile of the tensor-core kernel (0: more heads per group than it stacks)."""
+    return int(layers_lib().dl_window_tc_rows(heads, kv_heads))
+
+
+def window_tc_supported(heads: int, kv_heads: int, dim: int, rope_dims: int, cache_dtype) -> bool:
+    ctype = T_BF16 if cache_dtype == torch.bfloat16 else T_F32
+    return layers_lib().dl_window_attention_tc_supported(heads, kv_heads, dim, rope_dims, ctype) == 0
+
+
+def window_attention_tc(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, rope_dims: int, scale: float,
+                        softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor,
+                        tile_rows: torch.Tensor, n_tiles: int, rq: int):
+    """The tensor-core kernel over row tiles (tile_rows int32 [n_tiles][rq] on the device, -1 = no row)."""
+    a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache)
+    check_layers(layers_lib().dl_window_attention_tc(a, tile_rows.data_ptr(), n_tiles, rq, _stream()), "dl_window_attention_tc")
+    lib.count_launch()
+
+
+def window_attention_tiles(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, tiles):
+    """Convenience for callers with host-side tiles (lists of row indices of one sequence, consecutive positions)."""
+    rq = window_tc_rows(heads, kv_heads)
+    t = torch.full((len(tiles), rq), -1, dtype=torch.int32)
+    for i, rows in enumerate(tiles):
+        t[i, :len(rows)] = torch.tensor(rows, dtype=torch.int32)
+    window_attention_tc(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache,
+                        t.to(q.device), len(tiles), rq)
+
+
 # ---- routed experts ---------------------------------------------------------------------------------------------------
 def moe_select(z: torch.Tensor, M: int, experts: int, top: int, groups: int, keep: int, sel: torch.Tensor, wgt: torch.Tensor,
                group_top: int = 2, renorm: bool = False):
@@ -296,6 +325,66 @@ def moe_rows(w_up: torch.Tensor, w_down: torch.Tensor, x: torch.Tensor, M: int, 
     a.act, a.y, a.ldy = act.data_ptr(), y.data_ptr(), y.stride(0)
     check_layers(layers_lib().dl_moe_rows(a, _stream()), "dl_moe_rows")
     lib.count_launch(2)
+
+
+class MoeGrouped:
+    """The expert products of a routed feed-forward on the tensor cores: weight images of all experts (made once), the
+    scratch of the sorted rows, and the launch sequence  plan -> gather -> grouped GEMM (relu^2) -> image -> grouped GEMM
+    -> weighted combine.  Nothing returns to the host between the launches."""
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, top: int, max_rows: int):
+        Lb = layers_lib()
+        self.E, self.ff, self.width, self.top = w_up.shape[0], w_up.shape[1], w_up.shape[2], top
+        dev = w_up.device
+        self.up_bytes = int(Lb.dl_wh_bytes(self.ff, _round_up(self.width, 128)))
+        self.down_bytes = int(Lb.dl_wh_bytes(self.width, _round_up(self.ff, 128)))
+        self.wh_up = torch.empty(self.E * self.up_bytes, dtype=torch.uint8, device=dev)
+        self.wh_down = torch.empty(self.E * self.down_bytes, dtype=torch.uint8, device=dev)
+        for e in range(self.E):
+            check_layers(Lb.dl_wh_from_dense(w_up[e].data_ptr(), self.ff, self.width, w_up.stride(1),
+                                             self.wh_up[e * self.up_bytes:].data_ptr(), _stream()), "dl_wh_from_dense")
+            check_layers(Lb.dl_wh_from_dense(w_down[e].data_ptr(), self.width, self.ff, w_down.stride(1),
+                                             self.wh_down[e * self.down_bytes:].data_ptr(), _stream()), "dl_wh_from_dense")
+        self.max_rows = max_rows
+        self.cap = _round_up(max_rows * top + 8 * self.E, 8)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.cnt, self.grp = torch.zeros(self.E, **i32), torch.zeros(2 * self.E, **i32)
+        self.slot_row, self.pair_pos = torch.zeros(self.cap, **i32), torch.zeros(max_rows * top, **i32)
+        self.xh_in = torch.zeros(xh_bytes(self.width, self.cap), dtype=torch.uint8, device=dev)
+        self.xh_act = torch.zeros(xh_bytes(self.ff, self.cap), dtype=torch.uint8, device=dev)
+        self.act = torch.zeros(self.cap, self.ff, dtype=torch.float32, device=dev)
+        self.yp = torch.zeros(self.cap, self.width, dtype=torch.float32, device=dev)
+
+    def nbytes(self) -> int:
+        return self.wh_up.numel() + self.wh_down.numel()
+
+    def _gemm(self, wh, group_bytes, N, K, xh, y, M, epi):
+        e = DlEpilogue()
+        e.kind, e.n_dst, e.ld, e.dst_off = EPI_DENSE, 1, y.stride(0), 0
+        e.dst[0] = y.data_ptr()
+        e.dense_op, e.dense_param, e.dense_aux, e.dense_aux_ld = epi, 0.0, None, 0
+        check_layers(layers_lib().dl_gemm_wh_tc_grouped(wh.data_ptr(), group_bytes, self.E, self.grp.data_ptr(), N, _round_up(K, 128),
+                                                        xh.data_ptr(), self.cap, M, e, 2, _stream()), "dl_gemm_wh_tc_grouped")
+        lib.count_launch()
+
+    def run(self, x: torch.Tensor, M: int, sel: torch.Tensor, wgt: torch.Tensor, y: torch.Tensor):
+        """x [M][width] f32, sel / wgt [M][top] -> y [M][width]."""
+        Lb = layers_lib()
+        assert M <= self.max_rows
+        n_sorted = min(self.cap, _round_up(M * self.top + 7 * self.E, 8))          # sorted rows incl. padding, at most
+        a = DlMoePlanArgs()
+        a.sel, a.M, a.top, a.experts, a.cap = sel.data_ptr(), M, self.top, self.E, n_sorted
+        a.cnt, a.grp, a.slot_row, a.pair_pos = self.cnt.data_ptr(), self.grp.data_ptr(), self.slot_row.data_ptr(), self.pair_pos.data_ptr()
+        check_layers(Lb.dl_moe_plan(a, _stream()), "dl_moe_plan")
+        check_layers(Lb.dl_xh_gather_rows(x.data_ptr(), x.stride(0), self.slot_row.data_ptr(), n_sorted, self.width, self.cap,
+                                          self.xh_in.data_ptr(), _stream()), "dl_xh_gather_rows")
+        self._gemm(self.wh_up, self.up_bytes, self.ff, self.width, self.xh_in, self.act, M, DENSE_RELU2)
+        check_layers(Lb.dl_xh_from_rows(self.act.data_ptr(), self.act.stride(0), n_sorted, self.ff, self.cap, self.xh_act.data_ptr(),
+                                        _stream()), "dl_xh_from_rows")
+        self._gemm(self.wh_down, self.down_bytes, self.width, self.ff, self.xh_act, self.yp, M, DENSE_STORE)
+        check_layers(Lb.dl_moe_combine(self.yp.data_ptr(), self.yp.stride(0), self.pair_pos.data_ptr(), wgt.data_ptr(), M, self.top,
+                                       self.width, y.data_ptr(), y.stride(0), _stream()), "dl_moe_combine")
+        lib.count_launch(6)
 
 
 _ARGMAX_SCRATCH = {}

@@ -318,6 +318,12 @@ class DlMoeArgs(C.Structure):
                 ("act", C.c_void_p), ("y", C.c_void_p), ("ldy", C.c_longlong)]
 
 
+class DlMoePlanArgs(C.Structure):
+    """Mirror of ``DlMoePlanArgs``."""
+    _fields_ = [("sel", C.c_void_p), ("M", C.c_int), ("top", C.c_int), ("experts", C.c_int), ("cap", C.c_int),
+                ("cnt", C.c_void_p), ("grp", C.c_void_p), ("slot_row", C.c_void_p), ("pair_pos", C.c_void_p)]
+
+
 _layers = None
 
 
@@ -349,6 +355,13 @@ def layers_lib():
     L.dl_window_attention.argtypes = [C.POINTER(DlWindowAttnArgs), i32, vp]
     L.dl_moe_select.argtypes = [C.POINTER(DlMoeSelectArgs), vp]
     L.dl_moe_rows.argtypes = [C.POINTER(DlMoeArgs), vp]
+    L.dl_moe_plan.argtypes = [C.POINTER(DlMoePlanArgs), vp]
+    L.dl_moe_combine.argtypes = [vp, i64, vp, vp, i32, i32, i32, vp, i64, vp]
+    L.dl_xh_gather_rows.argtypes = [vp, i64, vp, i32, i32, i32, vp, vp]
+    L.dl_gemm_wh_tc_grouped.argtypes = [vp, i64, i32, vp, i32, i32, vp, i32, i32, C.POINTER(DlEpilogue), i32, vp]
+    L.dl_window_tc_rows.argtypes = [i32, i32]
+    L.dl_window_attention_tc_supported.argtypes = [i32, i32, i32, i32, i32]
+    L.dl_window_attention_tc.argtypes = [C.POINTER(DlWindowAttnArgs), vp, i32, i32, vp]
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
     L.dl_mamba_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), C.POINTER(DlMambaScanArgs), C.POINTER(DlMambaChunks), vp]
@@ -365,7 +378,9 @@ def layers_lib():
     L.dl_argmax_scratch_bytes.argtypes = [i32]
     for name in ("dl_dense", "dl_embed_rows", "dl_rms_norm", "dl_latent_kv_write", "dl_rope_rows", "dl_latent_attention", "dl_latent_attention_tc",
                  "dl_mamba_conv", "dl_mamba_scan", "dl_mamba_scan_chunked", "dl_sample_rows", "dl_argmax", "dl_wh_from_dense", "dl_xh_from_rows",
-                 "dl_gemm_wh_tc", "dl_hyper_step", "dl_window_kv_write", "dl_window_attention", "dl_moe_select", "dl_moe_rows"):
+                 "dl_gemm_wh_tc", "dl_hyper_step", "dl_window_kv_write", "dl_window_attention", "dl_moe_select", "dl_moe_rows", "dl_moe_plan",
+                 "dl_moe_combine", "dl_xh_gather_rows", "dl_gemm_wh_tc_grouped", "dl_window_tc_rows", "dl_window_attention_tc_supported",
+                 "dl_window_attention_tc"):
         getattr(L, name).restype = i32
     _layers = L
     return L

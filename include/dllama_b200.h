@@ -491,6 +491,28 @@ typedef struct {
     float* y; long long ldy;
 } DlMoeArgs;
 int dl_moe_rows(const DlMoeArgs* args /*host*/, void* stream);
+/* Grouped form for the tensor cores.  dl_moe_plan sorts the M * top (row, expert) pairs by expert (stable) into segments
+ * whose first rows are multiples of 8: grp[e] = {first sorted row, rows}, slot_row[i] = batch row of sorted row i (-1:
+ * padding, up to cap >= M * top + 7 * experts), pair_pos[m * top + k] = sorted row of the pair; cnt: scratch [experts].
+ * dl_xh_gather_rows builds the GEMM's activation image of the sorted rows, dl_gemm_wh_tc_grouped runs one product per
+ * segment against that expert's weight image, dl_moe_combine sums a row's `top` results weighted, in the order chosen. */
+typedef struct {
+    const int* sel; int M, top, experts, cap;
+    int* cnt; int* grp; int* slot_row; int* pair_pos;
+} DlMoePlanArgs;
+int dl_moe_plan(const DlMoePlanArgs* args /*host*/, void* stream);
+int dl_moe_combine(const float* yp, long long ldp, const int* pair_pos, const float* wgt, int M, int top, int width,
+                   float* y, long long ldy, void* stream);
+int dl_xh_gather_rows(const float* x, long long ldx, const int* rows /*device*/, int n_rows, int K, int ncap, uint8_t* xh,
+                      void* stream);
+int dl_gemm_wh_tc_grouped(const uint8_t* wh, long long wh_group_bytes, int n_groups, const int* grp /*device*/, int d, int n,
+                          const uint8_t* xh, int ncap, int max_group_rows, const DlEpilogue* epi /*host*/, int force_cg,
+                          void* stream);
+/* tensor-core windowed attention (bf16 cache): tiles of up to rq = dl_window_tc_rows() consecutive rows of one sequence,
+ * tile_rows[n_tiles][rq] (device; -1 where a tile has fewer rows) */
+int dl_window_tc_rows(int heads, int kv_heads);
+int dl_window_attention_tc_supported(int heads, int kv_heads, int dim, int rope_dims, int ctype);
+int dl_window_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* tile_rows, int n_tiles, int rq, void* stream);
 
 #ifdef __cplusplus
 }

@@ -56,3 +56,48 @@ def test_oracle_prefix_property():
     toks = torch.randint(0, 40, (20,), generator=torch.Generator().manual_seed(3)).tolist()
     a, b = O.model_logits(t, cfg, toks), O.model_logits(t, cfg, toks[:11])
     assert torch.allclose(a[:11], b, atol=1e-9)
+
+
+# ---- Sunesun: configuration, weight names, frequency table, the oracle's own window --------------------------------------
+def test_sunesun_configuration_weights_of_and_streams(tmp_path):
+    import sunesun_oracle as S
+    from dllama_b200.models.layered import example_config_sunesun, interpolated_rotary
+    cfg = example_config_sunesun(layers=3, streams=2)
+    d = str(tmp_path / "s")
+    tensors = write_random_model(d, cfg, seed=1)
+    assert registry.architecture_of(d) == "Sunesun" and "Sunesun" in registry.ARCHITECTURES
+    c = LayerListConfig.load(d)
+    assert (c.residual, c.streams, c.hyper_weights, c.embed_scale, c.residual_mult) == ("hyper", 2, True, 2.0, 0.5)
+    assert [l.weights_of for l in c.layers] == [None, None, 0]
+    assert "l2.mix.q" not in tensors and "l2.hc1.mix" not in tensors and tensors["l1.hc2.mix"].shape == (2, 2)
+    assert tensors["l0.mix.k"].shape == (3 * 32, 160) and tensors["l0.mlp.e11.down"].shape == (160, 64) and "l0.mix.v" not in tensors
+    plain = {k: v for k, v in cfg.items() if k != "streams"}
+    c2 = LayerListConfig.from_dict(plain)
+    assert c2.streams == 1 and not c2.hyper_weights and "l0.hc1.in" not in random_tensors(plain, seed=1)
+    bad = json.loads(json.dumps(cfg))
+    bad["layers"][1]["weights_of"] = 2                      # a layer that has no weights of its own
+    with pytest.raises(ValueError):
+        LayerListConfig.from_dict(bad)
+    # the engine's frequency table equals the oracle's angles
+    rot = cfg["layers"][0]["mixer"]["rot"]
+    f, mag = interpolated_rotary(rot["base"], rot["dims"], rot["scaling"])
+    cos, sin = S.rotary_table(rot, 50)
+    pos = torch.arange(50, dtype=torch.float64)[:, None]
+    assert torch.allclose(torch.cos(pos * f) * mag, cos, atol=1e-12) and torch.allclose(torch.sin(pos * f) * mag, sin, atol=1e-12)
+    assert mag > 1.0 and float(f[-1]) < rot["base"] ** (-2.0 * (rot["dims"] // 2 - 1) / rot["dims"])      # slow frequencies were divided
+
+
+def test_sunesun_oracle_window_and_prefix_property():
+    """The oracle itself: appended tokens change nothing before them, and a token outside every window changes nothing."""
+    import sunesun_oracle as S
+    from dllama_b200.models.layered import example_config_sunesun
+    cfg = example_config_sunesun(width=48, vocab=40, layers=2, heads=2, kv_heads=1, window=6, streams=3)
+    t = random_tensors(cfg, seed=2)
+    toks = torch.randint(0, 40, (30,), generator=torch.Generator().manual_seed(3)).tolist()
+    a, b = S.model_logits(t, cfg, toks), S.model_logits(t, cfg, toks[:11])
+    assert torch.allclose(a[:11], b, atol=1e-9)
+    other = list(toks)
+    other[3] = (toks[3] + 1) % 40
+    c = S.model_logits(t, cfg, other)
+    # two layers of window 6 reach 10 positions back: position 3 is seen up to position 13 and by nothing after it
+    assert not torch.allclose(a[13], c[13], atol=1e-9) and torch.allclose(a[14:], c[14:], atol=1e-9)
