@@ -24,65 +24,88 @@
 // ------------------------------------------------------------------------------------------------
 #define MS_WARPS 4
 
+// the best (value, index) over the warp: larger value first, lower index on ties; index -1 = nothing
+__device__ __forceinline__ void warp_best(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi < i))) { v = ov; i = oi; }
+    }
+}
+
+// One warp per row.  Scores sit in shared memory (taken ones are set to -1: sigmoid scores are >= 0); every pick is a
+// strided scan by the lanes and one warp reduction.
 __global__ void __launch_bounds__(MS_WARPS * 32) moe_select_kernel(DlMoeSelectArgs a) {
     extern __shared__ float sm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x * MS_WARPS + warp;
     if (m >= a.M) return;
-    const int E = a.experts, per = E / a.groups;
-    float* s = sm + (size_t)warp * (E + a.groups);        // [E] scores, then [groups] group scores (< 0: dropped)
-    float* gs = s + E;
-    for (int e = lane; e < E; e += 32) s[e] = sigmoid_f(a.z[(size_t)m * a.ldz + e]);
+    const int E = a.experts, G = a.groups, per = E / G;
+    float* s = sm + (size_t)warp * (2 * E + G);             // [E] scores, [E] working copy, [G] group scores (< 0: dropped)
+    float* w = s + E;
+    float* gs = w + E;
+    for (int e = lane; e < E; e += 32) w[e] = s[e] = sigmoid_f(a.z[(size_t)m * a.ldz + e]);
     __syncwarp();
-    for (int g = lane; g < a.groups; g += 32) {            // sum of the group's largest scores
-        float sum = 0.f, prev_v = INFINITY;
-        int prev_i = -1;
-        for (int k = 0; k < a.group_top && k < per; ++k) {      // next in the order (score down, index up)
-            int best = -1;
-            for (int i = 0; i < per; ++i) {
-                const float v = s[g * per + i];
-                const bool after_prev = v < prev_v || (v == prev_v && i > prev_i);
-                if (after_prev && (best < 0 || v > s[g * per + best])) best = i;
+    if (G > 1) {
+        for (int g = 0; g < G; ++g) {                        // the group's score: its group_top largest, picked off the copy
+            float sum = 0.f;
+            for (int k = 0; k < a.group_top && k < per; ++k) {
+                float bv = -1.f;
+                int bi = -1;
+                for (int i = lane; i < per; i += 32)
+                    if (w[g * per + i] >= 0.f && (bi < 0 || w[g * per + i] > bv)) { bv = w[g * per + i]; bi = i; }
+                warp_best(bv, bi);
+                sum += bv;
+                if (lane == 0) w[g * per + bi] = -1.f;
+                __syncwarp();
             }
-            prev_v = s[g * per + best];
-            prev_i = best;
-            sum += prev_v;
+            if (lane == 0) gs[g] = sum;
         }
-        gs[g] = sum;
-    }
+        __syncwarp();
+        for (int k = 0; k < G - a.keep; ++k) {               // drop the worst group; among equals the one with the higher index
+            float bv = 0.f;
+            int bi = -1;                                     // ordered by (-score down, G - 1 - g up)
+            for (int g = lane; g < G; g += 32) {
+                if (gs[g] < 0.f) continue;
+                const float v = -gs[g];
+                const int idx = G - 1 - g;
+                if (bi < 0 || v > bv || (v == bv && idx < bi)) { bv = v; bi = idx; }
+            }
+            warp_best(bv, bi);
+            if (lane == 0) gs[G - 1 - bi] = -1.f;
+            __syncwarp();
+        }
+    } else if (lane == 0) gs[0] = 0.f;
     __syncwarp();
-    if (lane == 0) {
-        // keep the best groups: mark the others
-        const int drop = a.groups - a.keep;
-        for (int k = 0; k < drop; ++k) {
-            int worst = -1;
-            for (int g = 0; g < a.groups; ++g)
-                if (gs[g] >= 0.f && (worst < 0 || gs[g] <= gs[worst])) worst = g;      // ties: the higher index goes first
-            gs[worst] = -1.f;
+    for (int e = lane; e < E; e += 32) w[e] = gs[e / per] >= 0.f ? s[e] : -1.f;      // eligible experts
+    __syncwarp();
+    float total = 0.f;
+    for (int k = 0; k < a.top; ++k) {
+        float bv = -1.f;
+        int bi = -1;
+        for (int e = lane; e < E; e += 32)
+            if (w[e] >= 0.f && (bi < 0 || w[e] > bv)) { bv = w[e]; bi = e; }
+        warp_best(bv, bi);
+        total += bv;
+        if (lane == 0) {
+            a.sel[(size_t)m * a.top + k] = bi;
+            a.wgt[(size_t)m * a.top + k] = bv;
+            w[bi] = -1.f;
         }
-        float total = 0.f;
-        for (int k = 0; k < a.top; ++k) {
-            int best = -1;
-            for (int e = 0; e < E; ++e)
-                if (gs[e / per] >= 0.f && s[e] >= 0.f && (best < 0 || s[e] > s[best])) best = e;
-            a.sel[(size_t)m * a.top + k] = best;
-            a.wgt[(size_t)m * a.top + k] = s[best];
-            total += s[best];
-            s[best] = -1.f;                                // sigmoid scores are >= 0: taken
-        }
-        if (a.renorm)
-            for (int k = 0; k < a.top; ++k) a.wgt[(size_t)m * a.top + k] /= total;
+        __syncwarp();
     }
+    if (a.renorm && lane < a.top) a.wgt[(size_t)m * a.top + lane] /= total;
 }
 
 extern "C" int dl_moe_select(const DlMoeSelectArgs* args, void* stream) {
     const DlMoeSelectArgs& a = *args;
     if (a.M < 1 || a.experts < 1 || a.groups < 1 || a.experts % a.groups || a.keep < 1 || a.keep > a.groups || a.top < 1 ||
-        a.top > a.keep * (a.experts / a.groups) || a.group_top < 1) {
+        a.top > a.keep * (a.experts / a.groups) || a.group_top < 1 || (a.renorm && a.top > 32)) {
         dl_set_error("dl_moe_select: %d experts in %d groups, keep %d, top %d", a.experts, a.groups, a.keep, a.top);
         return -1;
     }
-    const size_t smem = (size_t)MS_WARPS * (a.experts + a.groups) * sizeof(float);
+    const size_t smem = (size_t)MS_WARPS * (2 * a.experts + a.groups) * sizeof(float);
     if (smem > 48 * 1024) { dl_set_error("dl_moe_select: too many experts (%d)", a.experts); return -1; }
     moe_select_kernel<<<(a.M + MS_WARPS - 1) / MS_WARPS, MS_WARPS * 32, smem, (cudaStream_t)stream>>>(a);
     LAYER_CHECK_LAUNCH("dl_moe_select");
@@ -145,16 +168,46 @@ __global__ void __launch_bounds__(MR_WARPS * 32) moe_up_rows_kernel(DlMoeArgs a,
     }
 }
 
+// One warp per (row, output column): the row's experts are taken four at a time, their weight rows loaded side by side
+// (independent accumulators), then reduced and summed with the weights in the order the experts were chosen.
 template <typename WT, bool RX>
 __global__ void __launch_bounds__(MR_WARPS * 32) moe_down_rows_kernel(DlMoeArgs a, bool vec) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x, c = blockIdx.y * MR_WARPS + warp;
     if (c >= a.width) return;
     float out = 0.f;
-    for (int k = 0; k < a.top; ++k) {
-        const int pair = m * a.top + k, e = a.sel[pair];
-        const WT* w = (const WT*)a.w_down + ((size_t)e * a.width + c) * a.ff;
-        out = fmaf(a.wgt[pair], warp_dot<WT, RX>(w, a.act + (size_t)pair * a.ff, a.ff, vec, lane), out);
+    for (int k0 = 0; k0 < a.top; k0 += 4) {
+        const WT* w[4];
+        const float* x[4];
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int pair = m * a.top + min(k0 + j, a.top - 1);
+            w[j] = (const WT*)a.w_down + ((size_t)a.sel[pair] * a.width + c) * a.ff;
+            x[j] = a.act + (size_t)pair * a.ff;
+        }
+        if (vec) {
+#pragma unroll 4
+            for (int k = lane * 8; k < a.ff; k += 256) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float wv[8], xv[8];
+                    MoeVec<WT>::load8(w[j] + k, wv);
+                    MoeVec<float>::load8(x[j] + k, xv);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[j] = fmaf(RX ? round_bf16(xv[i]) : xv[i], wv[i], acc[j]);
+                }
+            }
+        } else {
+            for (int k = lane; k < a.ff; k += 32)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = fmaf(RX ? round_bf16(x[j][k]) : x[j][k], ld_f(w[j] + k), acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float d = warp_sum(acc[j]);
+            if (k0 + j < a.top) out = fmaf(a.wgt[m * a.top + k0 + j], d, out);
+        }
     }
     if (lane == 0) a.y[(size_t)m * a.ldy + c] = out;
 }

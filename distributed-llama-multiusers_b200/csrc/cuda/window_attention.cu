@@ -11,7 +11,8 @@
 // Rotary: interleaved pairs (2i, 2i + 1), angle = pos * freqs[i] formed in f64, cos and sin multiplied by rope_scale
 // (frequency interpolation schemes that also scale the rotation's magnitude pass their factor here).
 //
-// Kernels: the cache writer; the per-row attention kernel (exact f32 arithmetic on either cache type; one CTA per
+// Kernels: the cache writer, which also turns the queries in place (one launch, cos and sin formed once per row and
+// pair); the per-row attention kernel (exact f32 arithmetic on either cache type; one CTA per
 // (row, key/value head), all query heads of the group share each staged page; pages outside the window are never
 // touched); the tensor-core kernel for prompt portions (bf16 cache) further down.
 #include "mma_common.cuh"
@@ -22,33 +23,58 @@
 // ------------------------------------------------------------------------------------------------
 // cache writer
 // ------------------------------------------------------------------------------------------------
+// One CTA per row.  cos and sin of the row's angles are formed ONCE (f64) into shared memory; then every (head, pair) is
+// turned by its own thread: the query heads in place (when q is given), the key heads on their way into the cache; the
+// rest of each key is copied.
+#define WK_MAX_PAIRS 256
 template <typename CT>
-__global__ void __launch_bounds__(128) window_kv_write_kernel(DlWindowKvArgs a) {
+__global__ void __launch_bounds__(256) window_kv_write_kernel(DlWindowKvArgs a) {
+    __shared__ float cs[WK_MAX_PAIRS], sn[WK_MAX_PAIRS];
     const int m = blockIdx.x;
     const int pos = a.pos[m], slot = a.slot[m];
     const int page = a.block_table[(size_t)slot * a.max_pages + pos / WA_PAGE];
     const int LD = a.dim + a.rope_dims, half = a.rope_dims / 2;
-    for (int g = 0; g < a.kv_heads; ++g) {
-        const float* in = a.k + (size_t)m * a.ld + (size_t)g * a.dim;
-        CT* dst = (CT*)a.cache + (((size_t)page * a.kv_heads + g) * WA_PAGE + pos % WA_PAGE) * LD;
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            double s, c;
-            sincos((double)pos * a.freqs[i], &s, &c);
-            const double u = in[2 * i], v = in[2 * i + 1], ms = a.rope_scale;
-            st_f(dst + 2 * i, (float)((u * c - v * s) * ms));
-            st_f(dst + 2 * i + 1, (float)((v * c + u * s) * ms));
+    const float* kin = a.k + (size_t)m * a.ld;
+    CT* line0 = (CT*)a.cache + (((size_t)page * a.kv_heads) * WA_PAGE + pos % WA_PAGE) * LD;      // head g: + g * WA_PAGE * LD
+    const size_t head_step = (size_t)WA_PAGE * LD;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double sd, cd;
+        sincos((double)pos * a.freqs[i], &sd, &cd);
+        cs[i] = (float)(cd * (double)a.rope_scale);
+        sn[i] = (float)(sd * (double)a.rope_scale);
+    }
+    __syncthreads();
+    const int nq = a.q ? a.q_heads : 0;
+    for (int t = threadIdx.x; t < (a.kv_heads + nq) * half; t += blockDim.x) {
+        const int h = t / half, i = t - h * half;
+        const float c = cs[i], s = sn[i];
+        if (h < a.kv_heads) {
+            const float u = kin[h * a.dim + 2 * i], v = kin[h * a.dim + 2 * i + 1];
+            CT* dst = line0 + h * head_step;
+            st_f(dst + 2 * i, u * c - v * s);
+            st_f(dst + 2 * i + 1, v * c + u * s);
+            st_f(dst + a.dim + 2 * i, u);
+            st_f(dst + a.dim + 2 * i + 1, v);
+        } else {
+            float* q = a.q + (size_t)m * a.ldq + (size_t)(h - a.kv_heads) * a.dim;
+            const float u = q[2 * i], v = q[2 * i + 1];
+            q[2 * i] = u * c - v * s;
+            q[2 * i + 1] = v * c + u * s;
         }
-        for (int i = a.rope_dims + threadIdx.x; i < a.dim; i += blockDim.x) st_f(dst + i, in[i]);
-        for (int i = threadIdx.x; i < a.rope_dims; i += blockDim.x) st_f(dst + a.dim + i, in[i]);
+    }
+    const int rest = a.dim - a.rope_dims;
+    for (int t = threadIdx.x; t < a.kv_heads * rest; t += blockDim.x) {
+        const int g = t / rest, i = a.rope_dims + t - g * rest;
+        st_f(line0 + g * head_step + i, kin[g * a.dim + i]);
     }
 }
 
 extern "C" int dl_window_kv_write(const DlWindowKvArgs* args, int M, void* stream) {
     const DlWindowKvArgs& a = *args;
-    if (a.rope_dims > a.dim || (a.rope_dims & 1) || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: bad rotary or page size"); return -1; }
+    if (a.rope_dims > a.dim || (a.rope_dims & 1) || a.rope_dims > 2 * WK_MAX_PAIRS || a.page_size != WA_PAGE) { dl_set_error("dl_window_kv_write: bad rotary or page size"); return -1; }
     cudaStream_t st = (cudaStream_t)stream;
-    if (a.ctype == DL_T_BF16) window_kv_write_kernel<__nv_bfloat16><<<M, 128, 0, st>>>(a);
-    else window_kv_write_kernel<float><<<M, 128, 0, st>>>(a);
+    if (a.ctype == DL_T_BF16) window_kv_write_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(a);
+    else window_kv_write_kernel<float><<<M, 256, 0, st>>>(a);
     LAYER_CHECK_LAUNCH("dl_window_kv_write");
     return 0;
 }
@@ -150,7 +176,7 @@ extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* st
 // key/value head g; the heads/kv_heads query heads of the group read the same cache lines, so (position, head) pairs
 // stack on the M dimension of the MMA: 4 warps x 16 stacked rows.  The CTA walks the pages that the tile's windows
 // touch; per page (32 tokens), per warp:
-//     S[16 x 32]  = Q[16 x D] . K[32 x D]^T        Q fragments stay in registers (bf16), K by ldmatrix
+//     S[16 x 32]  = Q[16 x D] . K[32 x D]^T        Q (bf16, staged once per tile) and K by ldmatrix
 //     scale, soft cap, window mask, online softmax in f32 (two rows per thread, reduced over the quad)
 //     O[16 x D]  += P[16 x 32] . V[32 x D]         P from the score registers, V by ldmatrix.trans from the SAME staged
 //                                                  line: value column c sits at D + c (c < rope_dims) or at c
@@ -159,6 +185,10 @@ extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* st
 // ------------------------------------------------------------------------------------------------
 #define WM_ROWS 64
 
+// tanh(x) = 1 - 2 / (e^(2x) + 1) on the fast exponential: absolute error about 1e-7 (what the capped score needs), and
+// exact limits for large |x| (e^(2x) -> inf or 0)
+__device__ __forceinline__ float fast_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+
 __host__ __device__ __forceinline__ int wm_line_stride(int LD) {      // bf16 elements; rows 16 B apart modulo 128 B
     int s = (LD + 7) / 8 * 8 + 8;
     if ((s * 2) % 128 == 0) s += 8;
@@ -166,12 +196,15 @@ __host__ __device__ __forceinline__ int wm_line_stride(int LD) {      // bf16 el
 }
 
 template <int DK>
-__global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq) {
+__global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq,
+                                                                   int n_splits, float* __restrict__ partial) {
     constexpr int D = 16 * DK, NV = D / 8;
     extern __shared__ __align__(16) uint8_t smraw[];
     __shared__ int s_row[WM_ROWS];
     const int RD = a.rope_dims, LD = D + RD, LDS = wm_line_stride(LD);
+    constexpr int QS = D + 8;                                                       // row stride of the query tile (bf16)
     __nv_bfloat16* kv_s = reinterpret_cast<__nv_bfloat16*>(smraw);                  // [2][WA_PAGE][LDS]
+    __nv_bfloat16* q_s = kv_s + (size_t)2 * WA_PAGE * LDS;                          // [WM_ROWS][QS]: the stacked queries
     const int tile = blockIdx.x, g = blockIdx.y, rep = a.heads / a.kv_heads;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
     if (threadIdx.x < rq) s_row[threadIdx.x] = tile_rows[(size_t)tile * rq + threadIdx.x];
@@ -181,27 +214,31 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
     if (n_rows == 0) return;
     const int p_first = a.pos[s_row[0]], p_last = p_first + n_rows - 1, slot = a.slot[s_row[0]];
     const int lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
-    const int pg_lo = lo / WA_PAGE, pg_hi = p_last / WA_PAGE;
+    int pg_lo = lo / WA_PAGE, pg_hi = p_last / WA_PAGE;
+    if (n_splits > 1) {                  // this CTA's share of the tile's pages (possibly none)
+        const int per = (pg_hi - pg_lo + n_splits) / n_splits;
+        pg_lo += (int)blockIdx.z * per;
+        pg_hi = min(pg_hi, pg_lo + per - 1);
+    }
     const bool active = warp * 16 < n_rows * rep;
+    const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
 
     // this thread's two stacked rows: s = position-in-tile * rep + head-in-group
     const int s0 = warp * 16 + gid, s1 = s0 + 8;
     const int r0 = s0 / rep, r1 = s1 / rep;
     const bool ok0 = r0 < n_rows, ok1 = r1 < n_rows;
     const int pos0 = p_first + r0, pos1 = p_first + r1;
-    const size_t q_off0 = ok0 ? (size_t)s_row[r0] * a.ldq + (size_t)(g * rep + s0 % rep) * D : 0;
-    const size_t q_off1 = ok1 ? (size_t)s_row[r1] * a.ldq + (size_t)(g * rep + s1 % rep) * D : 0;
-    uint32_t qf[DK][4];
-#pragma unroll
-    for (int kk = 0; kk < DK; ++kk) {
-        const int c = kk * 16 + tig * 2;
-        float2 u0 = make_float2(0.f, 0.f), u1 = u0, v0 = u0, v1 = u0;
-        if (ok0) { u0 = *reinterpret_cast<const float2*>(a.q + q_off0 + c); v0 = *reinterpret_cast<const float2*>(a.q + q_off0 + c + 8); }
-        if (ok1) { u1 = *reinterpret_cast<const float2*>(a.q + q_off1 + c); v1 = *reinterpret_cast<const float2*>(a.q + q_off1 + c + 8); }
-        qf[kk][0] = pack_bf16(u0.x, u0.y);
-        qf[kk][1] = pack_bf16(u1.x, u1.y);
-        qf[kk][2] = pack_bf16(v0.x, v0.y);
-        qf[kk][3] = pack_bf16(v1.x, v1.y);
+    // the tile's queries, rounded to bf16, into shared memory (A fragments come from there by ldmatrix: registers are
+    // what limits the CTAs per SM)
+    for (int idx = threadIdx.x; idx < WM_ROWS * (D / 4); idx += 128) {
+        const int sr = idx / (D / 4), c4 = idx - sr * (D / 4);
+        const int r = sr / rep;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < n_rows) v = *reinterpret_cast<const float4*>(a.q + (size_t)s_row[r] * a.ldq + (size_t)(g * rep + sr % rep) * D + c4 * 4);
+        uint2 pk;
+        pk.x = pack_bf16(v.x, v.y);
+        pk.y = pack_bf16(v.z, v.w);
+        *reinterpret_cast<uint2*>(q_s + (size_t)sr * QS + c4 * 4) = pk;
     }
     float o[NV][4];
 #pragma unroll
@@ -218,12 +255,12 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
             cp_async16(dst + (size_t)j * LDS + part * 8, src + (size_t)j * LD + part * 8);
         }
     };
-    issue(pg_lo, 0);
+    if (pg_lo <= pg_hi) issue(pg_lo, 0);
     const int mat = lane >> 3, rr = lane & 7;
     for (int pg = pg_lo; pg <= pg_hi; ++pg) {
         const int buf = (pg - pg_lo) & 1;
         cp_async_wait_all();
-        __syncthreads();                      // page pg has landed; everyone is done with the other buffer
+        __syncthreads();                      // page pg has landed (and the queries); everyone is done with the other buffer
         if (pg < pg_hi) issue(pg + 1, buf ^ 1);
         if (!active) continue;
         const __nv_bfloat16* kv = kv_s + (size_t)buf * WA_PAGE * LDS;
@@ -232,12 +269,14 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
         for (int n = 0; n < 4; ++n) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f; }
 #pragma unroll
         for (int kk = 0; kk < DK; ++kk) {
+            uint32_t qf[4];
+            ldmatrix_x4(qf, q_s + (size_t)(warp * 16 + (mat & 1) * 8 + rr) * QS + kk * 16 + (mat >> 1) * 8);
 #pragma unroll
             for (int np = 0; np < 2; ++np) {
                 uint32_t b[4];
                 ldmatrix_x4(b, kv + (size_t)(np * 16 + (mat >> 1) * 8 + rr) * LDS + kk * 16 + (mat & 1) * 8);
-                mma_bf16(sc[2 * np], qf[kk], b[0], b[1]);
-                mma_bf16(sc[2 * np + 1], qf[kk], b[2], b[3]);
+                mma_bf16(sc[2 * np], qf, b[0], b[1]);
+                mma_bf16(sc[2 * np + 1], qf, b[2], b[3]);
             }
         }
         // scale, soft cap, mask
@@ -250,7 +289,7 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
                 const int pr = (e < 2) ? pos0 : pos1;
                 const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window);
                 float s = sc[n][e] * a.scale;
-                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+                if (a.softcap > 0.f) s = a.softcap * fast_tanh(s * inv_cap);
                 s = vis ? s : -INFINITY;
                 sc[n][e] = s;
                 if (e < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
@@ -259,14 +298,14 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float al0 = (m0 == -INFINITY) ? 0.f : expf(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : expf(m1 - mn1);
+        const float al0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mn1);
         const float ref0 = (mn0 == -INFINITY) ? 0.f : mn0, ref1 = (mn1 == -INFINITY) ? 0.f : mn1;      // a row that sees nothing yet: every p = 0
         m0 = mn0; m1 = mn1;
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
-            sc[n][0] = expf(sc[n][0] - ref0); sc[n][1] = expf(sc[n][1] - ref0);
-            sc[n][2] = expf(sc[n][2] - ref1); sc[n][3] = expf(sc[n][3] - ref1);
+            sc[n][0] = __expf(sc[n][0] - ref0); sc[n][1] = __expf(sc[n][1] - ref0);
+            sc[n][2] = __expf(sc[n][2] - ref1); sc[n][3] = __expf(sc[n][3] - ref1);
             ps0 += sc[n][0] + sc[n][1];
             ps1 += sc[n][2] + sc[n][3];
         }
@@ -295,6 +334,22 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
     if (!active) return;
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (n_splits > 1) {                  // unnormalised sums, running maximum and sum per stacked row, for the merge kernel
+        float* base = partial + (((size_t)tile * a.kv_heads + g) * n_splits + blockIdx.z) * WM_ROWS * (D + 2);
+        if (ok0) {
+            float* dst = base + (size_t)s0 * (D + 2);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][0], o[v][1]);
+            if (tig == 0) { dst[D] = m0; dst[D + 1] = l0; }
+        }
+        if (ok1) {
+            float* dst = base + (size_t)s1 * (D + 2);
+#pragma unroll
+            for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][2], o[v][3]);
+            if (tig == 0) { dst[D] = m1; dst[D + 1] = l1; }
+        }
+        return;
+    }
     if (ok0) {
         float* dst = a.out + (size_t)s_row[r0] * a.ldo + (size_t)(g * rep + s0 % rep) * D;
         const float inv = 1.f / l0;
@@ -306,6 +361,50 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(DlWindowAttnA
         const float inv = 1.f / l1;
 #pragma unroll
         for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][2] * inv, o[v][3] * inv);
+    }
+}
+
+// merge of the page shares: one CTA per (tile, key/value head, position of the tile).  The shares' maxima and sums are
+// gathered into shared memory, every (head, share) weight e^(m_k - m) / l is formed once, then a thread per (head,
+// column) sums the shares.
+#define WM_MAX_SPLITS 32
+__global__ void __launch_bounds__(128) window_merge_kernel(DlWindowAttnArgs a, const int* __restrict__ tile_rows, int rq, int n_splits,
+                                                           const float* __restrict__ partial) {
+    __shared__ float w_s[WM_ROWS * WM_MAX_SPLITS], l_s[WM_ROWS * WM_MAX_SPLITS];
+    const int tile = blockIdx.x, g = blockIdx.y, r = blockIdx.z, D = a.dim, rep = a.heads / a.kv_heads;
+    const int m = tile_rows[(size_t)tile * rq + r];
+    if (m < 0) return;
+    const float* base = partial + ((size_t)tile * a.kv_heads + g) * n_splits * WM_ROWS * (D + 2);
+    for (int idx = threadIdx.x; idx < rep * n_splits; idx += blockDim.x) {
+        const int hg = idx / n_splits, k = idx - hg * n_splits;
+        const float* p = base + ((size_t)k * WM_ROWS + r * rep + hg) * (D + 2);
+        w_s[idx] = p[D];
+        l_s[idx] = p[D + 1];
+    }
+    __syncthreads();
+    for (int hg = threadIdx.x; hg < rep; hg += blockDim.x) {
+        float mx = -INFINITY, l = 0.f;
+        for (int k = 0; k < n_splits; ++k) mx = fmaxf(mx, w_s[hg * n_splits + k]);
+        for (int k = 0; k < n_splits; ++k) {
+            const float mk = w_s[hg * n_splits + k];
+            const float e = mk == -INFINITY ? 0.f : expf(mk - mx);
+            l += l_s[hg * n_splits + k] * e;
+            w_s[hg * n_splits + k] = e;
+        }
+        const float inv = 1.f / l;
+        for (int k = 0; k < n_splits; ++k) w_s[hg * n_splits + k] *= inv;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rep * D; idx += blockDim.x) {
+        const int hg = idx / D, c = idx - hg * D;
+        const float* p = base + (size_t)(r * rep + hg) * (D + 2) + c;
+        float acc = 0.f;
+#pragma unroll 4
+        for (int k = 0; k < n_splits; ++k) {
+            const float wk = w_s[hg * n_splits + k];
+            if (wk != 0.f) acc = fmaf(wk, p[(size_t)k * WM_ROWS * (D + 2)], acc);
+        }
+        a.out[(size_t)m * a.ldo + (size_t)(g * rep + hg) * D + c] = acc;
     }
 }
 
@@ -323,24 +422,38 @@ extern "C" int dl_window_attention_tc_supported(int heads, int kv_heads, int dim
     return 0;
 }
 
-extern "C" int dl_window_attention_tc(const DlWindowAttnArgs* args, const int* tile_rows, int n_tiles, int rq, void* stream) {
+// floats of the scratch that n_splits > 1 needs
+extern "C" long long dl_window_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int dim) {
+    return (long long)n_tiles * kv_heads * n_splits * WM_ROWS * (dim + 2);
+}
+
+// n_splits > 1 (few tiles, e.g. decoding): grid.z CTAs share a tile's pages and leave partial sums in `partial`
+// (dl_window_tc_partial_floats() f32) that a merge launch combines.
+extern "C" int dl_window_attention_tc(const DlWindowAttnArgs* args, const int* tile_rows, int n_tiles, int rq, int n_splits,
+                                      float* partial, void* stream) {
     const DlWindowAttnArgs& a = *args;
     if (window_args_ok(a, "dl_window_attention_tc")) return -1;
     if (dl_window_attention_tc_supported(a.heads, a.kv_heads, a.dim, a.rope_dims, a.ctype) != 0 || rq < 1 || rq > dl_window_tc_rows(a.heads, a.kv_heads) ||
-        (a.ldq & 1) || (a.ldo & 1)) {
+        (a.ldq & 3) || (a.ldo & 1) || ((uintptr_t)a.q & 15)) {
         dl_set_error("dl_window_attention_tc: sizes not supported (heads %d / %d, dim %d, rotary %d, rq %d)", a.heads, a.kv_heads, a.dim, a.rope_dims, rq);
         return -1;
     }
     if (n_tiles < 1) return 0;
-    const size_t smem = (size_t)2 * WA_PAGE * wm_line_stride(a.dim + a.rope_dims) * sizeof(__nv_bfloat16);
-    dim3 grid(n_tiles, a.kv_heads);
+    if (n_splits < 1 || n_splits > WM_MAX_SPLITS || (n_splits > 1 && partial == nullptr)) { dl_set_error("dl_window_attention_tc: n_splits %d without scratch", n_splits); return -1; }
+    const size_t smem = ((size_t)2 * WA_PAGE * wm_line_stride(a.dim + a.rope_dims) + (size_t)WM_ROWS * (a.dim + 8)) * sizeof(__nv_bfloat16);
+    dim3 grid(n_tiles, a.kv_heads, n_splits);
     cudaStream_t st = (cudaStream_t)stream;
     switch (a.dim / 16) {
-#define WM_CASE(DK_) case DK_: window_attention_mma_kernel<DK_><<<grid, 128, smem, st>>>(a, tile_rows, rq); break;
+#define WM_CASE(DK_)                                                                                                      \
+    case DK_:                                                                                                             \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(window_attention_mma_kernel<DK_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        window_attention_mma_kernel<DK_><<<grid, 128, smem, st>>>(a, tile_rows, rq, n_splits, partial);                  \
+        break;
         WM_CASE(1) WM_CASE(2) WM_CASE(3) WM_CASE(4) WM_CASE(6) WM_CASE(8)
 #undef WM_CASE
         default: dl_set_error("dl_window_attention_tc: dim %d", a.dim); return -1;
     }
+    if (n_splits > 1) window_merge_kernel<<<dim3(n_tiles, a.kv_heads, rq), 128, 0, st>>>(a, tile_rows, rq, n_splits, partial);
     LAYER_CHECK_LAUNCH("dl_window_attention_tc");
     return 0;
 }

@@ -155,6 +155,8 @@ TC_MIN_ROWS = int(os.environ.get("DLLAMA_LAYERS_TC_MIN_ROWS", "32"))
 CHUNKED_SCAN_MIN_ROWS = 256  # a batch holding this many rows of one sequence runs the recurrence chunk-parallel
 TC_HEADS_MIN_ROWS = 256      # per-head products (one small GEMM per head) take the tensor-core path from this many rows
 GRAPH_MAX_ROWS = 64          # batches up to this many rows are replayed from CUDA graphs
+WINDOW_MAX_SPLITS = 32       # most CTAs that share one tile's pages in the windowed-attention kernel
+WINDOW_CTAS_PER_SM = 8       # pages are shared until about this many CTAs per SM run (one page in flight per CTA)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -348,13 +350,19 @@ class WindowAttentionMixer:
         H, G, d, rd = self.H, self.G, self.dim, self.rope_dims
         qk, o = e.buf("qk", (H + G) * d), e.buf("o", H * d)
         e.mm(self.w_qk, h, qk, M, src="h")
-        if rd:
-            L.rope_rows(qk, M, H, d, 0, rd, self.freqs, e.pos, interleaved=True, mag=self.rope_mag)
-        L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache)
+        # one launch: the keys go into the cache (rotated key + unrotated head) and the queries are rotated in place
+        L.window_kv_write(qk[:, H * d:], M, G, d, rd, self.freqs, self.rope_mag, e.pos, e.slot, e.block_table, self.cache,
+                          q=qk, q_heads=H)
         if self.tc_rq:
             tile_rows, n_tiles = e.window_tiles(self.tc_rq)
+            # few tiles (decoding): several CTAs share a tile's pages.  The share count depends on the tiling only (not on
+            # the positions), so a captured graph stays valid as the sequences grow
+            pages = (self.window + PAGE - 1) // PAGE + 1 if self.window else e.max_pages
+            n_splits = 1
+            if n_tiles * G <= 2 * e.n_sms:
+                n_splits = max(1, min(pages, WINDOW_MAX_SPLITS, (WINDOW_CTAS_PER_SM * e.n_sms) // (n_tiles * G)))
             L.window_attention_tc(qk, o, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
-                                  self.cache, tile_rows, n_tiles, self.tc_rq)
+                                  self.cache, tile_rows, n_tiles, self.tc_rq, n_splits, e.window_partial(d) if n_splits > 1 else None)
         else:
             L.window_attention(qk, o, M, H, G, d, rd, self.scale, self.softcap, self.window, e.pos, e.slot, e.block_table,
                                self.cache)
@@ -558,6 +566,10 @@ class LayerListEngine:
         self._chunks_off = self._tiles_off + R + 16 * S      # then chunk_seq | chunk_off [max_chunks] of the chunked scan
         self._desc_len = self._chunks_off + 2 * self._max_chunks
         # then, per tile height rq of the windowed-attention layers, tile_rows [tiles][rq] of their tensor-core kernel
+        self._window_partial = None
+        wd = [mx.dim for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq]
+        if wd:
+            self.window_partial(max(wd))               # allocated before any graph is captured
         self._wtile_off: Dict[int, int] = {}
         self._wtile_n: Dict[int, int] = {}
         for rq in sorted({mx.tc_rq for mx in mixers if isinstance(mx, WindowAttentionMixer) and mx.tc_rq}):
@@ -643,6 +655,13 @@ class LayerListEngine:
         if not self.attn_rq or not L.latent_tc_supported(mx.H, mx.rank, mx.dr, self.wdtype, self.attn_rq):
             return None
         return (self.tile_rows, self._n_tiles, self.attn_rq, self._n_splits, self._attn_partial)
+
+    def window_partial(self, dim: int) -> torch.Tensor:
+        """Scratch of the windowed-attention kernel's page shares: tiles x key/value heads x shares <= WINDOW_CTAS_PER_SM x SMs."""
+        need = self.L.window_tc_partial_floats(WINDOW_CTAS_PER_SM * self.n_sms, 1, 1, dim)
+        if self._window_partial is None or self._window_partial.numel() < need:
+            self._window_partial = torch.zeros(need, dtype=torch.float32, device=self.device)
+        return self._window_partial
 
     def window_tiles(self, rq: int):
         """(tile_rows on the device, tiles) of this batch for windowed-attention layers with tiles of rq rows."""

@@ -246,9 +246,12 @@ def hyper_step(x: torch.Tensor, M: int, streams: int, dim: int, y: Optional[torc
 
 # ---- sliding-window attention whose values are its keys ---------------------------------------------------------------
 def window_kv_write(k: torch.Tensor, M: int, kv_heads: int, dim: int, rope_dims: int, freqs: torch.Tensor, rope_scale: float,
-                    pos, slot, block_table: torch.Tensor, cache: torch.Tensor):
+                    pos, slot, block_table: torch.Tensor, cache: torch.Tensor, q: Optional[torch.Tensor] = None, q_heads: int = 0):
+    """Keys into the paged cache (rotated key + unrotated head per line); with q [M][q_heads * dim] the queries are
+    rotated in place by the same launch."""
     a = DlWindowKvArgs()
     a.k, a.ld, a.kv_heads, a.dim, a.rope_dims = k.data_ptr(), k.stride(0), kv_heads, dim, rope_dims
+    a.q, a.ldq, a.q_heads = _p(q), (q.stride(0) if q is not None else 0), q_heads
     a.freqs, a.rope_scale = freqs.data_ptr(), rope_scale
     a.pos, a.slot, a.block_table = pos.data_ptr(), slot.data_ptr(), block_table.data_ptr()
     a.max_pages, a.page_size = block_table.shape[1], PAGE_SIZE
@@ -286,23 +289,35 @@ def window_tc_supported(heads: int, kv_heads: int, dim: int, rope_dims: int, cac
     return layers_lib().dl_window_attention_tc_supported(heads, kv_heads, dim, rope_dims, ctype) == 0
 
 
+def window_tc_partial_floats(n_tiles: int, kv_heads: int, n_splits: int, dim: int) -> int:
+    return int(layers_lib().dl_window_tc_partial_floats(n_tiles, kv_heads, n_splits, dim))
+
+
 def window_attention_tc(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, rope_dims: int, scale: float,
                         softcap: float, window: int, pos, slot, block_table: torch.Tensor, cache: torch.Tensor,
-                        tile_rows: torch.Tensor, n_tiles: int, rq: int):
-    """The tensor-core kernel over row tiles (tile_rows int32 [n_tiles][rq] on the device, -1 = no row)."""
+                        tile_rows: torch.Tensor, n_tiles: int, rq: int, n_splits: int = 1, partial: Optional[torch.Tensor] = None):
+    """The tensor-core kernel over row tiles (tile_rows int32 [n_tiles][rq] on the device, -1 = no row).  n_splits > 1:
+    that many CTAs share each tile's pages (few tiles: decoding) and a merge launch follows; partial: f32 scratch."""
     a = _window_args(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache)
-    check_layers(layers_lib().dl_window_attention_tc(a, tile_rows.data_ptr(), n_tiles, rq, _stream()), "dl_window_attention_tc")
-    lib.count_launch()
+    if n_splits > 1:
+        assert partial is not None and partial.numel() >= window_tc_partial_floats(n_tiles, kv_heads, n_splits, dim)
+    check_layers(layers_lib().dl_window_attention_tc(a, tile_rows.data_ptr(), n_tiles, rq, n_splits, _p(partial), _stream()),
+                 "dl_window_attention_tc")
+    lib.count_launch(2 if n_splits > 1 else 1)
 
 
-def window_attention_tiles(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, tiles):
+def window_attention_tiles(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache, tiles,
+                           n_splits: int = 1):
     """Convenience for callers with host-side tiles (lists of row indices of one sequence, consecutive positions)."""
     rq = window_tc_rows(heads, kv_heads)
     t = torch.full((len(tiles), rq), -1, dtype=torch.int32)
     for i, rows in enumerate(tiles):
         t[i, :len(rows)] = torch.tensor(rows, dtype=torch.int32)
+    partial = None
+    if n_splits > 1:
+        partial = torch.zeros(window_tc_partial_floats(len(tiles), kv_heads, n_splits, dim), dtype=torch.float32, device=q.device)
     window_attention_tc(q, out, heads, kv_heads, dim, rope_dims, scale, softcap, window, pos, slot, block_table, cache,
-                        t.to(q.device), len(tiles), rq)
+                        t.to(q.device), len(tiles), rq, n_splits, partial)
 
 
 # ---- routed experts ---------------------------------------------------------------------------------------------------

@@ -288,7 +288,8 @@ class DlHyperArgs(C.Structure):
 
 class DlWindowKvArgs(C.Structure):
     """Mirror of ``DlWindowKvArgs``."""
-    _fields_ = [("k", C.c_void_p), ("ld", C.c_longlong), ("kv_heads", C.c_int), ("dim", C.c_int), ("rope_dims", C.c_int),
+    _fields_ = [("k", C.c_void_p), ("ld", C.c_longlong), ("q", C.c_void_p), ("ldq", C.c_longlong), ("q_heads", C.c_int),
+                ("kv_heads", C.c_int), ("dim", C.c_int), ("rope_dims", C.c_int),
                 ("freqs", C.c_void_p), ("rope_scale", C.c_float),
                 ("pos", C.c_void_p), ("slot", C.c_void_p), ("block_table", C.c_void_p),
                 ("max_pages", C.c_int), ("page_size", C.c_int), ("cache", C.c_void_p), ("ctype", C.c_int)]
@@ -361,7 +362,9 @@ def layers_lib():
     L.dl_gemm_wh_tc_grouped.argtypes = [vp, i64, i32, vp, i32, i32, vp, i32, i32, C.POINTER(DlEpilogue), i32, vp]
     L.dl_window_tc_rows.argtypes = [i32, i32]
     L.dl_window_attention_tc_supported.argtypes = [i32, i32, i32, i32, i32]
-    L.dl_window_attention_tc.argtypes = [C.POINTER(DlWindowAttnArgs), vp, i32, i32, vp]
+    L.dl_window_attention_tc.argtypes = [C.POINTER(DlWindowAttnArgs), vp, i32, i32, i32, vp, vp]
+    L.dl_window_tc_partial_floats.argtypes = [i32, i32, i32, i32]
+    L.dl_window_tc_partial_floats.restype = i64
     L.dl_mamba_conv.argtypes = [C.POINTER(DlMambaBatch), i32, i32, vp, i64, i32, vp, vp, i32, vp, vp, i32, i32, vp]
     L.dl_mamba_scan.argtypes = [C.POINTER(DlMambaBatch), i32, C.POINTER(DlMambaScanArgs), vp]
     L.dl_mamba_scan_chunked.argtypes = [C.POINTER(DlMambaBatch), C.POINTER(DlMambaScanArgs), C.POINTER(DlMambaChunks), vp]

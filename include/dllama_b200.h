@@ -449,6 +449,7 @@ int dl_hyper_step(const DlHyperArgs* args /*host*/, void* stream);
  * rope_dims].  Rotary: interleaved pairs, angle pos * freqs[i] (f64 [rope_dims / 2]), cos and sin times rope_scale. */
 typedef struct {
     const float* k; long long ld;             /* [M][kv_heads * dim] projected keys, unrotated */
+    float* q; long long ldq; int q_heads;     /* optional: [M][q_heads * dim] queries, rotated in place by the same launch */
     int kv_heads, dim, rope_dims;
     const double* freqs; float rope_scale;
     const int* pos; const int* slot; const int* block_table;
@@ -512,7 +513,10 @@ int dl_gemm_wh_tc_grouped(const uint8_t* wh, long long wh_group_bytes, int n_gro
  * tile_rows[n_tiles][rq] (device; -1 where a tile has fewer rows) */
 int dl_window_tc_rows(int heads, int kv_heads);
 int dl_window_attention_tc_supported(int heads, int kv_heads, int dim, int rope_dims, int ctype);
-int dl_window_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* tile_rows, int n_tiles, int rq, void* stream);
+/* n_splits > 1: that many CTAs share each tile's pages; partial: dl_window_tc_partial_floats() f32 of scratch */
+long long dl_window_tc_partial_floats(int n_tiles, int kv_heads, int n_splits, int dim);
+int dl_window_attention_tc(const DlWindowAttnArgs* args /*host*/, const int* tile_rows, int n_tiles, int rq, int n_splits,
+                           float* partial, void* stream);
 
 #ifdef __cplusplus
 }
