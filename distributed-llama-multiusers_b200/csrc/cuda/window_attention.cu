@@ -177,7 +177,7 @@ extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* st
 // stack on the M dimension of the MMA: 4 warps x 16 stacked rows.  The CTA walks the pages that the tile's windows
 // touch; per page (32 tokens), per warp:
 //     S[16 x 32]  = Q[16 x D] . K[32 x D]^T        Q (bf16, staged once per tile) and K by ldmatrix
-//     scale, soft cap, window mask, online softmax in f32 (two rows per thread, reduced over the quad)
+//     scale, soft cap, window mask, online softmax in f32 and base 2 (two rows per thread, reduced over the quad)
 //     O[16 x D]  += P[16 x 32] . V[32 x D]         P from the score registers, V by ldmatrix.trans from the SAME staged
 //                                                  line: value column c sits at D + c (c < rope_dims) or at c
 // mma.sync m16n8k16 bf16, f32 accumulators.  Pages arrive by cp.async into two buffers (page k + 1 in flight while
@@ -185,9 +185,23 @@ extern "C" int dl_window_attention(const DlWindowAttnArgs* args, int M, void* st
 // ------------------------------------------------------------------------------------------------
 #define WM_ROWS 64
 
-// tanh(x) = 1 - 2 / (e^(2x) + 1) on the fast exponential: absolute error about 1e-7 (what the capped score needs), and
-// exact limits for large |x| (e^(2x) -> inf or 0)
-__device__ __forceinline__ float fast_tanh(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+// The softmax of the tensor-core kernel works in base 2: a score leaves this function already multiplied by log2(e), so a
+// probability is one ex2.  With a soft cap, cap * tanh(x / cap) = cap * (1 - 2 / (e^(2x/cap) + 1)) (absolute error about
+// 1e-7 of the cap on the fast exponential and reciprocal; exact limits for large |x|):
+//     c1 = scale * 2 / cap * log2(e),  K = cap * log2(e):   score2 = K - 2K / (2^(acc * c1) + 1)
+// without one: score2 = acc * (scale * log2(e)).
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+#define WM_LOG2E 1.4426950408889634f
+#define WM_LN2 0.6931471805599453f
 
 __host__ __device__ __forceinline__ int wm_line_stride(int LD) {      // bf16 elements; rows 16 B apart modulo 128 B
     int s = (LD + 7) / 8 * 8 + 8;
@@ -221,7 +235,9 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
         pg_hi = min(pg_hi, pg_lo + per - 1);
     }
     const bool active = warp * 16 < n_rows * rep;
-    const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+    const bool capped = a.softcap > 0.f;
+    const float c1 = capped ? a.scale * 2.f / a.softcap * WM_LOG2E : a.scale * WM_LOG2E;
+    const float capK = a.softcap * WM_LOG2E;
 
     // this thread's two stacked rows: s = position-in-tile * rep + head-in-group
     const int s0 = warp * 16 + gid, s1 = s0 + 8;
@@ -279,33 +295,37 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
                 mma_bf16(sc[2 * np + 1], qf, b[2], b[3]);
             }
         }
-        // scale, soft cap, mask
+        // scale and soft cap (base-2 scores), window mask (skipped on pages that every row of the tile sees whole)
+        const int pg_first = pg * WA_PAGE;
+        const bool whole = pg_first + WA_PAGE - 1 <= p_first && (a.window == 0 || p_last - pg_first < a.window) && n_rows * rep >= WM_ROWS;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = pg * WA_PAGE + n * 8 + tig * 2 + (e & 1);
-                const int pr = (e < 2) ? pos0 : pos1;
-                const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window);
-                float s = sc[n][e] * a.scale;
-                if (a.softcap > 0.f) s = a.softcap * fast_tanh(s * inv_cap);
-                s = vis ? s : -INFINITY;
-                sc[n][e] = s;
-                if (e < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
+                float s2 = sc[n][e] * c1;
+                if (capped) s2 = fmaf(-2.f * capK, fast_rcp(fast_ex2(s2) + 1.f), capK);
+                if (!whole) {
+                    const int j = pg_first + n * 8 + tig * 2 + (e & 1);
+                    const int pr = (e < 2) ? pos0 : pos1;
+                    const bool vis = ((e < 2) ? ok0 : ok1) && j <= pr && (a.window == 0 || pr - j < a.window);
+                    s2 = vis ? s2 : -INFINITY;
+                }
+                sc[n][e] = s2;
+                if (e < 2) mx0 = fmaxf(mx0, s2); else mx1 = fmaxf(mx1, s2);
             }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float al0 = (m0 == -INFINITY) ? 0.f : __expf(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : __expf(m1 - mn1);
+        const float al0 = (m0 == -INFINITY) ? 0.f : fast_ex2(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : fast_ex2(m1 - mn1);
         const float ref0 = (mn0 == -INFINITY) ? 0.f : mn0, ref1 = (mn1 == -INFINITY) ? 0.f : mn1;      // a row that sees nothing yet: every p = 0
         m0 = mn0; m1 = mn1;
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
-            sc[n][0] = __expf(sc[n][0] - ref0); sc[n][1] = __expf(sc[n][1] - ref0);
-            sc[n][2] = __expf(sc[n][2] - ref1); sc[n][3] = __expf(sc[n][3] - ref1);
+            sc[n][0] = fast_ex2(sc[n][0] - ref0); sc[n][1] = fast_ex2(sc[n][1] - ref0);
+            sc[n][2] = fast_ex2(sc[n][2] - ref1); sc[n][3] = fast_ex2(sc[n][3] - ref1);
             ps0 += sc[n][0] + sc[n][1];
             ps1 += sc[n][2] + sc[n][3];
         }
@@ -340,13 +360,13 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
             float* dst = base + (size_t)s0 * (D + 2);
 #pragma unroll
             for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][0], o[v][1]);
-            if (tig == 0) { dst[D] = m0; dst[D + 1] = l0; }
+            if (tig == 0) { dst[D] = m0 * WM_LN2; dst[D + 1] = l0; }
         }
         if (ok1) {
             float* dst = base + (size_t)s1 * (D + 2);
 #pragma unroll
             for (int v = 0; v < NV; ++v) *reinterpret_cast<float2*>(dst + v * 8 + tig * 2) = make_float2(o[v][2], o[v][3]);
-            if (tig == 0) { dst[D] = m1; dst[D + 1] = l1; }
+            if (tig == 0) { dst[D] = m1 * WM_LN2; dst[D + 1] = l1; }
         }
         return;
     }
