@@ -418,12 +418,9 @@ __global__ void __launch_bounds__(128) window_merge_kernel(DlWindowAttnArgs a, c
     for (int idx = threadIdx.x; idx < rep * D; idx += blockDim.x) {
         const int hg = idx / D, c = idx - hg * D;
         const float* p = base + (size_t)(r * rep + hg) * (D + 2) + c;
-        float acc = 0.f;
-#pragma unroll 4
-        for (int k = 0; k < n_splits; ++k) {
-            const float wk = w_s[hg * n_splits + k];
-            if (wk != 0.f) acc = fmaf(wk, p[(size_t)k * WM_ROWS * (D + 2)], acc);
-        }
+        float acc = 0.f;                      // a share without pages left zeros and weighs 0: every load can go out at once
+#pragma unroll 8
+        for (int k = 0; k < n_splits; ++k) acc = fmaf(w_s[hg * n_splits + k], p[(size_t)k * WM_ROWS * (D + 2)], acc);
         a.out[(size_t)m * a.ldo + (size_t)(g * rep + hg) * D + c] = acc;
     }
 }
