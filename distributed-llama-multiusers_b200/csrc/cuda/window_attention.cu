@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(128, 4) window_attention_mma_kernel(DlWindowAt
         }
         // scale and soft cap (base-2 scores), window mask (skipped on pages that every row of the tile sees whole)
         const int pg_first = pg * WA_PAGE;
-        const bool whole = pg_first + WA_PAGE - 1 <= p_first && (a.window == 0 || p_last - pg_first < a.window) && n_rows * rep >= WM_ROWS;
+        const bool whole = pg_first + WA_PAGE - 1 <= p_first && (a.window == 0 || p_last - pg_first < a.window);      // stacked rows without a position are never stored
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {

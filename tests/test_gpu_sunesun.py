@@ -235,15 +235,16 @@ def _attention_case(ctype, H, G, d, rd, window, softcap, n_ctx, queries, boost, 
     return seen
 
 
-WINDOW_QUERIES = [  # window 40: (position, boosted key)
-    (0, 0), (1, 0), (5, 5), (39, 0), (40, 0), (40, 1), (41, 1), (41, 2), (63, 24), (63, 23), (64, 25), (64, 24),
-    (95, 56), (96, 57), (96, 56), (200, 161), (200, 160), (200, 199), (200, 200), (255, 216), (255, 215), (255, 31), (255, 0)]
+WINDOW = 41
+WINDOW_QUERIES = [  # (position, boosted key): at distance 0, WINDOW - 1 (the last one seen) and WINDOW (the first one not seen)
+    (0, 0), (1, 0), (5, 5), (40, 0), (41, 0), (41, 1), (42, 1), (42, 2), (63, 23), (63, 22), (64, 24), (64, 23),
+    (95, 55), (96, 56), (96, 55), (200, 160), (200, 159), (200, 199), (200, 200), (255, 215), (255, 214), (255, 31), (255, 0)]
 
 
 @pytest.mark.parametrize("ctype", [torch.float32, torch.bfloat16])
 def test_window_attention_sees_exactly_its_window(ctype):
-    seen = _attention_case(ctype, H=4, G=2, d=24, rd=8, window=40, softcap=50.0, n_ctx=256, queries=WINDOW_QUERIES, boost=25.0)
-    assert seen == [0 <= p - b < 40 for p, b in WINDOW_QUERIES]
+    seen = _attention_case(ctype, H=6, G=2, d=24, rd=8, window=WINDOW, softcap=50.0, n_ctx=256, queries=WINDOW_QUERIES, boost=25.0)
+    assert seen == [0 <= p - b < WINDOW for p, b in WINDOW_QUERIES] and seen.count(False) == 9
     # window a multiple of the page, one key/value head per head, everything rotated; window 1: only itself
     _attention_case(ctype, H=3, G=3, d=16, rd=16, window=32, softcap=0.0, n_ctx=130,
                     queries=[(31, 0), (32, 0), (32, 1), (64, 32), (64, 33), (129, 98), (129, 97)], boost=20.0)
@@ -253,8 +254,8 @@ def test_window_attention_sees_exactly_its_window(ctype):
 
 
 def test_window_attention_on_the_tensor_cores_sees_exactly_its_window():
-    seen = _attention_case(torch.bfloat16, H=4, G=2, d=32, rd=8, window=40, softcap=50.0, n_ctx=256, queries=WINDOW_QUERIES, boost=25.0, tc=True)
-    assert seen == [0 <= p - b < 40 for p, b in WINDOW_QUERIES]
+    seen = _attention_case(torch.bfloat16, H=6, G=2, d=32, rd=8, window=WINDOW, softcap=50.0, n_ctx=256, queries=WINDOW_QUERIES, boost=25.0, tc=True)
+    assert seen == [0 <= p - b < WINDOW for p, b in WINDOW_QUERIES]
     _attention_case(torch.bfloat16, H=3, G=3, d=16, rd=16, window=32, softcap=0.0, n_ctx=130,
                     queries=[(31, 0), (32, 0), (32, 1), (64, 32), (64, 33), (129, 98), (129, 97)], boost=20.0, tc=True)
     _attention_case(torch.bfloat16, H=8, G=2, d=64, rd=64, window=0, softcap=30.0, n_ctx=600, queries=[(599, 0), (599, 3), (300, 299), (32, 31)], boost=25.0, tc=True)
@@ -266,7 +267,7 @@ def test_window_attention_tiles_of_rows_on_the_tensor_cores():
     from dllama_b200.models.layered import interpolated_rotary
     from dllama_b200.ops import layers as L
     g = torch.Generator().manual_seed(8)
-    for H, G, d, rd, window, cap in ((4, 2, 32, 8, 40, 20.0), (6, 3, 48, 48, 33, 0.0), (8, 1, 64, 16, 0, 30.0), (2, 2, 96, 32, 64, 0.0)):
+    for H, G, d, rd, window, cap in ((6, 2, 32, 8, 41, 25.0), (6, 3, 48, 48, 33, 0.0), (8, 1, 64, 16, 0, 30.0), (2, 2, 96, 32, 64, 0.0)):
         n_ctx = 200
         f, mag = interpolated_rotary(3000.0, rd, {"factor": 3.0, "original": 32, "fast": 4.0, "slow": 1.0})
         n_pages = (n_ctx + PAGE - 1) // PAGE
@@ -295,7 +296,7 @@ def test_window_attention_tiles_of_rows_on_the_tensor_cores():
             assert torch.allclose(got[rows], want[rows], atol=2e-2, rtol=2e-2), (H, G, d, n_splits, (got[rows] - want[rows]).abs().max())
 
 
-@pytest.mark.parametrize("E,top,count,keep", [(12, 3, 3, 2), (8, 4, 2, 1), (5, 2, 1, 1), (16, 16, 4, 4), (6, 2, 6, 3), (64, 6, 8, 4), (3, 1, 1, 1)])
+@pytest.mark.parametrize("E,top,count,keep", [(12, 3, 3, 2), (10, 4, 2, 1), (5, 2, 1, 1), (16, 16, 4, 4), (6, 2, 6, 3), (64, 6, 8, 4), (3, 1, 1, 1)])
 def test_routing_picks_the_best_experts_of_the_best_groups(E, top, count, keep):
     from dllama_b200.ops import layers as L
     g = torch.Generator().manual_seed(E * 7 + top)
@@ -323,7 +324,7 @@ def test_routing_can_drop_the_single_best_expert():
 
 
 @pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,W,ff,E,top", [(1, 88, 40, 5, 2), (7, 72, 24, 4, 4), (70, 160, 56, 12, 3), (300, 320, 96, 8, 4)])
+@pytest.mark.parametrize("M,W,ff,E,top", [(1, 88, 40, 5, 2), (7, 72, 24, 4, 4), (70, 160, 56, 12, 3), (300, 288, 104, 8, 3)])
 def test_expert_products_both_forms(wdtype, M, W, ff, E, top):
     """The per-pair form (any weights) and, for bf16 weights, the grouped tensor-core form against the oracle."""
     from dllama_b200.ops import layers as L
