@@ -4,7 +4,7 @@
 (attention_kernel, split-KV), and a 32-row sampling call (sample_kernel).
 
   python scripts/profile_misc.py                                       (plain run, must exit 0)
-  ncu --set full --clock-control none --import-source on -k regex:'attention_prefill_tc|attention_kernel|reduce_norm_quant|sample_kernel' -c 14 -o out python scripts/profile_misc.py
+  ncu --set full --clock-control none -k regex:'attention_prefill_tc|attention_kernel|reduce_norm_quant|sample_kernel' -c 14 -o out python scripts/profile_misc.py
 """
 import os
 import sys
