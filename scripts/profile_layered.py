@@ -1,0 +1,88 @@
+#!/usr/bin/env python3
+"""Workloads for launch lists and counter captures of the layer-list models (one GPU).
+
+  python scripts/profile_layered.py steps --design sunesun --size w2048
+      one 2048-token prompt per slot, then decode steps of 1 and of 32 rows, launched eagerly (no CUDA graphs) so that
+      every kernel shows in a launch list:
+        ncu --metrics gpu__time_duration.sum --clock-control none --csv --log-file out.csv python scripts/profile_layered.py steps ...
+  python scripts/profile_layered.py window-attention
+      the windowed-attention tile kernel alone (2048 rows of one sequence, 16 / 8 heads of 128, 64 rotated dims, window
+      1024, soft cap 50), timed with CUDA events; small enough for a full counter capture:
+        ncu --set full --clock-control none -k regex:window_attention_mma -s 1 -c 2 -o out python scripts/profile_layered.py window-attention
+Run the plain command first; capture only if it exits 0.
+"""
+import argparse
+import math
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def steps(a):
+    os.environ["DLLAMA_LAYERS_GRAPHS"] = "0"
+    import numpy as np
+    import torch
+    import bench
+    from dllama_b200.models import registry
+    from dllama_b200.models.layered import write_random_model
+    T, users, vocab, nl = a.prompt, 32, 32768, a.layers
+    d = os.path.join(a.model_dir, f"dllama_b200_{'layered' if a.design == 'ribivik' else a.design}_{a.size}_l{nl}")
+    if not os.path.exists(os.path.join(d, "model.safetensors")):
+        cfg = bench.layered_config(bench.LAYERED_SIZES[a.size], nl, vocab) if a.design == "ribivik" else bench.sunesun_config(a.size, nl, vocab)
+        write_random_model(d, cfg, seed=1)
+    torch.cuda.set_device(0)
+    eng = registry.engine_for_dir(d, max_rows=T, n_slots=users, max_seq_len=T + 64, dtype="bfloat16")
+    prompt = np.random.default_rng(0).integers(1, vocab, T).tolist()
+    slots = [eng.alloc_slot() for _ in range(users)]
+    for s in slots:
+        eng.forward(prompt, list(range(T)), [s] * T, logits_from=T - 1)
+    torch.cuda.synchronize()
+    print("prompts done: %d forwards of %d rows" % (users, T))
+    for i in range(3):
+        eng.decode_step_greedy([1], [T + i], [slots[0]])
+    torch.cuda.synchronize()
+    print("3 decode steps of 1 row done")
+    for i in range(2):
+        eng.decode_step_greedy([1] * users, [T + 3 + i] + [T + i] * (users - 1), slots)
+    torch.cuda.synchronize()
+    print("2 decode steps of %d rows done" % users)
+
+
+def window_attention(a):
+    import torch
+    from dllama_b200.models.layered import interpolated_rotary
+    from dllama_b200.ops import layers as L
+    H, G, d, rd, window, cap, n = 16, 8, 128, 64, 1024, 50.0, 2048
+    f, mag = interpolated_rotary(10000.0, rd, None)
+    n_pages = n // 32
+    bt = torch.arange(n_pages, dtype=torch.int32).view(1, -1).cuda()
+    cache = torch.zeros(n_pages, G, 32, d + rd, dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator().manual_seed(1)
+    k, q = torch.randn(n, G * d, generator=g).cuda(), torch.randn(n, H * d, generator=g).cuda()
+    pos, slot = torch.arange(n, dtype=torch.int32).cuda(), torch.zeros(n, dtype=torch.int32).cuda()
+    L.window_kv_write(k, n, G, d, rd, f.cuda(), mag, pos, slot, bt, cache, q=q, q_heads=H)
+    out = torch.zeros(n, H * d, device="cuda")
+    rq = L.window_tc_rows(H, G)
+    tiles = torch.arange(n, dtype=torch.int32).view(-1, rq).cuda()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(4):
+        ev0.record()
+        L.window_attention_tc(q, out, H, G, d, rd, 1 / math.sqrt(d), cap, window, pos, slot, bt, cache, tiles, n // rq, rq)
+        ev1.record()
+        torch.cuda.synchronize()
+        print("window attention: %.1f us" % (ev0.elapsed_time(ev1) * 1e3))
+    keys = sum(min(i + 1, window) for i in range(n))
+    print("GFLOP over the visible keys: %.2f" % (keys * H * d * 4 / 1e9))
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("what", choices=("steps", "window-attention"))
+    ap.add_argument("--design", default="sunesun", choices=("ribivik", "sunesun"))
+    ap.add_argument("--size", default="w2048")
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--model-dir", default="/tmp")
+    a = ap.parse_args()
+    steps(a) if a.what == "steps" else window_attention(a)
