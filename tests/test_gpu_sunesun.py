@@ -531,3 +531,80 @@ def test_the_command_line_serves_the_model_directory(model_a):
     s = eng.alloc_slot()
     lg = eng.prefill(s, reqs[2])
     _assert_close(lg.cpu(), want[2][-1:], F32_TOL, "prefill() of the engine surface")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# random configurations: sizes, layer lists and schedules drawn from a seed (f32, row by row against the oracle)
+# ---------------------------------------------------------------------------------------------------------------------
+def _random_config(rng):
+    import json
+    layers = []
+    for i in range(rng.randint(1, 4)):
+        own = [j for j in range(i) if "weights_of" not in layers[j]]
+        if own and rng.random() < 0.3:
+            j = rng.choice(own)
+            layers.append({**json.loads(json.dumps(layers[j])), "weights_of": j})
+            continue
+        G, rep = rng.choice([1, 2, 3, 4]), rng.choice([1, 2, 3, 5, 8])
+        dim = rng.choice([16, 24, 48, 64, 80, 96, 128])
+        rd = rng.choice([d for d in (0, 2, 8, 16, 24, 64, dim) if d <= dim])
+        m = _mixer(heads=G * rep, kv_heads=G, dim=dim, rot_dims=rd, window=rng.choice([0, 1, 2, 7, 31, 32, 33, 65, 100]),
+                   softcap=rng.choice([0, 5.0, 50.0]), scaling=bool(rd) and rng.random() < 0.7)
+        mlp = None
+        if rng.random() < 0.85:
+            count, per = rng.choice([1, 2, 4]), rng.choice([1, 2, 3])
+            keep = rng.randint(1, count)
+            mlp = _moe(experts=count * per, top=rng.randint(1, keep * per), count=count, keep=keep, ff=rng.choice([16, 40, 130]))
+        layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    cfg = {"architecture": "Sunesun", "width": rng.choice([64, 100, 136, 192]), "vocab": rng.choice([97, 300, 513]),
+           "norm": {"eps": 1e-5}, "embedding": {"scale": rng.choice([1.0, 2.5])}, "residual_mult": rng.choice([1.0, 0.4]), "layers": layers}
+    streams = rng.choice([0, 1, 2, 3, 4, 8])
+    if streams:
+        cfg["streams"] = streams
+    return cfg
+
+
+def _random_schedule(rng, lens):
+    left, steps, live, pending = list(lens), [], [], list(range(len(lens)))
+    while pending or live:
+        while pending and len(live) < 3 and (not live or rng.random() < 0.7):
+            live.append(pending.pop(0))
+        step = []
+        for i in list(live):
+            if rng.random() < 0.2 and len(live) > 1:
+                continue                                                # a request sits a step out
+            n = min(left[i], rng.choice([1, 1, 1, 2, 3, 17, 32, 33, 64, 90]))
+            step.append((i, n))
+            left[i] -= n
+            if left[i] == 0:
+                live.remove(i)
+        if step:
+            steps.append(step)
+    return steps
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_random_configurations_and_schedules(tmp_path, seed):
+    import random
+    from dllama_b200.models.layered import write_random_model
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    tensors = write_random_model(str(tmp_path / "m"), cfg, seed=seed)
+    g = torch.Generator().manual_seed(seed)
+    lens = [rng.choice([1, 5, 40, 70, 130]) for _ in range(4)]
+    reqs = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in lens]
+    want = [O.model_logits(tensors, cfg, r) for r in reqs]
+    n_pages = 3 * (max(lens) + 64) // PAGE
+    eng = _engine(str(tmp_path / "m"), max_rows=n_pages * PAGE, n_slots=3, seq=n_pages * PAGE, n_pages=n_pages)
+    got = _replay(eng, reqs, _random_schedule(rng, lens))
+    for i in got:
+        assert got[i].shape[0] == lens[i]
+        _assert_close(got[i], want[i], F32_TOL, f"seed {seed}, request {i}: {cfg['layers']}")
+    assert len(eng.pages.free_pages) == n_pages and len(eng.pages.free_slots) == 3
+    eng.close()
+    # the same model in bf16: fed in the schedule or whole, a row comes out the same
+    eng = _engine(str(tmp_path / "m"), "bfloat16", max_rows=n_pages * PAGE, n_slots=3, seq=n_pages * PAGE, n_pages=n_pages)
+    got = _replay(eng, reqs, _random_schedule(random.Random(seed + 100), lens))
+    whole = _replay(eng, reqs, [[(i, n)] for i, n in enumerate(lens)])
+    for i in got:
+        _assert_same(got[i], whole[i], f"seed {seed}, request {i} in bf16", tol=0.03)
