@@ -451,7 +451,7 @@ class _Layer:
             self.hc1 = _HyperWeights(eng, p + "hc1." if eng.cfg.hyper_weights else None)
         self.ff = None
         if spec.mlp is not None:
-            kind = spec.mlp.get("kind", "dense")
+            kind = spec.mlp.get("kind") or ("moe" if "router" in spec.mlp else "dense")
             if kind not in FEED_FORWARDS:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
             self.ff = FEED_FORWARDS[kind](eng, i, spec.mlp, p + "mlp.")
@@ -962,7 +962,7 @@ def random_tensors(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
                 t[p + "norm2b"] = small(W)
             elif S:
                 hyper(p + "hc2.")
-            if l["mlp"].get("kind", "dense") == "moe":
+            if (l["mlp"].get("kind") or ("moe" if "router" in l["mlp"] else "dense")) == "moe":
                 E, ff = l["mlp"]["router"]["experts"], l["mlp"]["expert"]["ff"]
                 t[p + "mlp.router"] = mat(E, W, 2.0)
                 for n in range(E):
