@@ -500,12 +500,15 @@ class LayerListEngine:
             self.embed = self.weight("embed")
             if tuple(self.embed.shape) != (self.cfg.vocab, self.cfg.width):
                 raise ValueError(f"embed has shape {tuple(self.embed.shape)}")
-            self.layers: List[_Layer] = []
+            # layers with weights of their own first: a looped layer may name a layer before or after itself
+            built: Dict[int, _Layer] = {i: _Layer(self, i, spec) for i, spec in enumerate(self.cfg.layers) if spec.weights_of is None}
             for i, spec in enumerate(self.cfg.layers):
-                owner = self.layers[spec.weights_of] if spec.weights_of is not None else None
-                if owner is not None and (spec.type, spec.mlp is None) != (self.cfg.layers[spec.weights_of].type, owner.ff is None):
-                    raise ValueError(f"layer {i}: its entry differs from layer {spec.weights_of}, whose weights it uses")
-                self.layers.append(_Layer(self, i, spec, owner))
+                if spec.weights_of is not None:
+                    owner = built[spec.weights_of]
+                    if (spec.type, spec.mlp is None) != (self.cfg.layers[spec.weights_of].type, owner.ff is None):
+                        raise ValueError(f"layer {i}: its entry differs from layer {spec.weights_of}, whose weights it uses")
+                    built[i] = _Layer(self, i, spec, owner)
+            self.layers: List[_Layer] = [built[i] for i in range(len(self.cfg.layers))]
             self.final_norm, self.head = self.vector("final.norm"), self.dense_weight(self.weight("head"))
         finally:
             self._st.close()

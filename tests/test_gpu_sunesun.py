@@ -402,6 +402,18 @@ def test_other_numbers_of_streams(tmp_path, variant):
     _assert_close(got[0], want, F32_TOL, variant)
 
 
+def test_a_looped_layer_may_come_before_the_layer_whose_weights_it_runs(tmp_path):
+    from dllama_b200.models.layered import write_random_model
+    cfg = _cfg_plain()
+    cfg["streams"] = 2
+    cfg["layers"] = [{**cfg["layers"][1], "weights_of": 1}, cfg["layers"][1], cfg["layers"][0]]
+    tensors = write_random_model(str(tmp_path / "m"), cfg, seed=13)
+    assert "l0.mix.q" not in tensors and "l1.mix.q" in tensors
+    req = torch.randint(0, cfg["vocab"], (40,), generator=torch.Generator().manual_seed(3)).tolist()
+    got = _replay(_engine(str(tmp_path / "m")), [req], [[(0, 33)], [(0, 7)]])
+    _assert_close(got[0], O.model_logits(tensors, cfg, req), F32_TOL, "forward reference")
+
+
 def test_prefill_then_token_by_token(model_a):
     path, cfg, tensors, reqs, want = model_a
     eng = _engine(path)
