@@ -14,9 +14,10 @@
 #define HC_THREADS 256
 #define HC_CACHE 16                 // columns per thread kept in registers (dim <= 4096); wider rows recompute
 
+template <int MAXS>
 __global__ void __launch_bounds__(HC_THREADS) hc_step_kernel(DlHyperArgs a) {
     __shared__ float red[32];
-    __shared__ float c_mix[DL_HC_MAX_STREAMS * DL_HC_MAX_STREAMS], c_out[DL_HC_MAX_STREAMS], c_in[DL_HC_MAX_STREAMS];
+    __shared__ float c_mix[MAXS * MAXS], c_out[MAXS], c_in[MAXS];
     const int m = blockIdx.x, S = a.streams, dim = a.dim;
     const bool write = a.y != nullptr, read = a.h != nullptr;
     if (threadIdx.x < S * S && write) c_mix[threadIdx.x] = a.mix[threadIdx.x];
@@ -33,30 +34,30 @@ __global__ void __launch_bounds__(HC_THREADS) hc_step_kernel(DlHyperArgs a) {
     float ss = 0.f;
     // one column: the old copies in, the new copies out (a write), the mixed value of the (new) copies back
     auto column = [&](int i) -> float {
-        float xs[DL_HC_MAX_STREAMS];
+        float xs[MAXS];
 #pragma unroll
-        for (int s = 0; s < DL_HC_MAX_STREAMS; ++s) xs[s] = s < S ? x[(size_t)s * dim + i] : 0.f;
+        for (int s = 0; s < MAXS; ++s) xs[s] = s < S ? x[(size_t)s * dim + i] : 0.f;
         if (write) {
             const float yv = y[i];
-            float xn[DL_HC_MAX_STREAMS];
+            float xn[MAXS];
 #pragma unroll
-            for (int t = 0; t < DL_HC_MAX_STREAMS; ++t) {
+            for (int t = 0; t < MAXS; ++t) {
                 xn[t] = 0.f;
                 if (t < S) {
                     float v = 0.f;
 #pragma unroll
-                    for (int s = 0; s < DL_HC_MAX_STREAMS; ++s)
+                    for (int s = 0; s < MAXS; ++s)
                         if (s < S) v = fmaf(c_mix[s * S + t], xs[s], v);
                     xn[t] = fmaf(c_out[t], yv, v);
                     x[(size_t)t * dim + i] = xn[t];
                 }
             }
 #pragma unroll
-            for (int s = 0; s < DL_HC_MAX_STREAMS; ++s) xs[s] = xn[s];
+            for (int s = 0; s < MAXS; ++s) xs[s] = xn[s];
         }
         float u = 0.f;
 #pragma unroll
-        for (int s = 0; s < DL_HC_MAX_STREAMS; ++s)
+        for (int s = 0; s < MAXS; ++s)
             if (s < S) u = fmaf(c_in[s], xs[s], u);
         return u;
     };
@@ -107,6 +108,7 @@ __global__ void __launch_bounds__(HC_THREADS) hc_step_kernel(DlHyperArgs a) {
 
 // The same with four columns per thread and step (dim % 4 == 0, 16-byte aligned rows): all copies of a column group are
 // loaded at once, so a decoding row is two or three dependent memory round trips instead of one per column.
+#define HC_VEC_STREAMS 8            // copies the four-column kernel keeps in registers; more copies take the scalar kernel
 #define HC_CACHE4 4                 // float4 groups per thread kept in registers (dim <= 4096)
 
 __device__ __forceinline__ float4 f4_fma(float a, float4 x, float4 acc) {
@@ -115,7 +117,7 @@ __device__ __forceinline__ float4 f4_fma(float a, float4 x, float4 acc) {
 
 __global__ void __launch_bounds__(HC_THREADS) hc_step_vec_kernel(DlHyperArgs a) {
     __shared__ float red[32];
-    __shared__ float c_mix[DL_HC_MAX_STREAMS * DL_HC_MAX_STREAMS], c_out[DL_HC_MAX_STREAMS], c_in[DL_HC_MAX_STREAMS];
+    __shared__ float c_mix[HC_VEC_STREAMS * HC_VEC_STREAMS], c_out[HC_VEC_STREAMS], c_in[HC_VEC_STREAMS];
     const int m = blockIdx.x, S = a.streams, dim = a.dim, n4 = dim >> 2;
     const bool write = a.y != nullptr, read = a.h != nullptr;
     if (threadIdx.x < S * S && write) c_mix[threadIdx.x] = a.mix[threadIdx.x];
@@ -134,29 +136,29 @@ __global__ void __launch_bounds__(HC_THREADS) hc_step_vec_kernel(DlHyperArgs a) 
         const int i = threadIdx.x + k * HC_THREADS;
         float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n4) {
-            float4 xs[DL_HC_MAX_STREAMS];
+            float4 xs[HC_VEC_STREAMS];
 #pragma unroll
-            for (int s = 0; s < DL_HC_MAX_STREAMS; ++s) xs[s] = s < S ? x[(size_t)s * n4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < HC_VEC_STREAMS; ++s) xs[s] = s < S ? x[(size_t)s * n4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
             if (write) {
                 const float4 yv = y[i];
-                float4 xn[DL_HC_MAX_STREAMS];
+                float4 xn[HC_VEC_STREAMS];
 #pragma unroll
-                for (int t = 0; t < DL_HC_MAX_STREAMS; ++t) {
+                for (int t = 0; t < HC_VEC_STREAMS; ++t) {
                     xn[t] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (t < S) {
                         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                        for (int s = 0; s < DL_HC_MAX_STREAMS; ++s)
+                        for (int s = 0; s < HC_VEC_STREAMS; ++s)
                             if (s < S) v = f4_fma(c_mix[s * S + t], xs[s], v);
                         xn[t] = f4_fma(c_out[t], yv, v);
                         x[(size_t)t * n4 + i] = xn[t];
                     }
                 }
 #pragma unroll
-                for (int s = 0; s < DL_HC_MAX_STREAMS; ++s) xs[s] = xn[s];
+                for (int s = 0; s < HC_VEC_STREAMS; ++s) xs[s] = xn[s];
             }
 #pragma unroll
-            for (int s = 0; s < DL_HC_MAX_STREAMS; ++s)
+            for (int s = 0; s < HC_VEC_STREAMS; ++s)
                 if (s < S) u = f4_fma(c_in[s], xs[s], u);
         }
         u_keep[k] = u;
@@ -189,10 +191,11 @@ extern "C" int dl_hyper_step(const DlHyperArgs* args, void* stream) {
     if (a.y && a.rows) { dl_set_error("dl_hyper_step: a row gather cannot come with a write"); return -1; }
     if (!a.y && !a.h) { dl_set_error("dl_hyper_step: nothing to do"); return -1; }
     const auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
-    const bool vec = a.dim % 4 == 0 && a.dim <= 4 * HC_THREADS * HC_CACHE4 && a.ldx % 4 == 0 && al16(a.x) &&
+    const bool vec = a.streams <= HC_VEC_STREAMS && a.dim % 4 == 0 && a.dim <= 4 * HC_THREADS * HC_CACHE4 && a.ldx % 4 == 0 && al16(a.x) &&
                      (!a.y || (a.ldy % 4 == 0 && al16(a.y))) && (!a.h || (a.ldh % 4 == 0 && al16(a.h))) && al16(a.norm_w) && al16(a.u_out);
     if (vec) hc_step_vec_kernel<<<a.M, HC_THREADS, 0, (cudaStream_t)stream>>>(a);
-    else hc_step_kernel<<<a.M, HC_THREADS, 0, (cudaStream_t)stream>>>(a);
+    else if (a.streams <= 8) hc_step_kernel<8><<<a.M, HC_THREADS, 0, (cudaStream_t)stream>>>(a);
+    else hc_step_kernel<DL_HC_MAX_STREAMS><<<a.M, HC_THREADS, 0, (cudaStream_t)stream>>>(a);
     LAYER_CHECK_LAUNCH("dl_hyper_step");
     return 0;
 }

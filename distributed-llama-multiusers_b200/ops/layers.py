@@ -15,7 +15,7 @@ from .lib import (DENSE_RELU2, DENSE_SIGMOID_MUL, DENSE_SOFTCAP, DENSE_STORE, EP
                   DlMoePlanArgs, DlMoeSelectArgs, DlNormArgs, DlWindowAttnArgs, DlWindowKvArgs, check_layers, layers_lib)
 
 PAGE_SIZE = 32
-HC_MAX_STREAMS = 8           # DL_HC_MAX_STREAMS of the hyper-connection kernel
+HC_MAX_STREAMS = 16          # DL_HC_MAX_STREAMS of the hyper-connection kernel
 
 
 def _stream() -> int:

@@ -431,7 +431,7 @@ int dl_mamba_scan_chunked(const DlMambaBatch* batch /*host*/, const DlMambaScanA
  * read  (h != NULL):  u = sum_s w_in[s] x_s (w_in NULL: ones);  h[m] = u / sqrt(mean(u^2) + eps) * norm_w (NULL: 1)
  * Both in one launch: the write of one sublayer with the read of the next.  `rows` gathers source rows (read only).
  * streams = 1, mix = w_out = {1}: the plain residual sum x += mult * y. */
-#define DL_HC_MAX_STREAMS 8
+#define DL_HC_MAX_STREAMS 16
 typedef struct {
     float* x; long long ldx;
     int streams, dim, M;

@@ -119,7 +119,7 @@ def _assert_same(got, ref, what, tol=0.02):
 # ---------------------------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ---------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("S,dim", [(1, 40), (2, 72), (4, 333), (5, 4500), (8, 64)])
+@pytest.mark.parametrize("S,dim", [(1, 40), (2, 72), (4, 333), (5, 4500), (8, 64), (11, 96), (16, 50)])
 def test_hyper_connection_write_read_and_both_at_once(S, dim):
     from dllama_b200.ops import layers as L
     g = torch.Generator().manual_seed(S * 100 + dim)
